@@ -1,0 +1,132 @@
+/* C ABI of libnanov41_b200.so: the B200 (sm_100a) MoE expert path of nanov41.
+ *
+ * The reference is pure Python; its plugin boundary is the monkey-patched `MoE.forward`
+ * (nanov41/fast_moe.py:478-488, nanov41/moe_triton.py:42-56) over Triton/TileLang kernels.
+ * These entry points are what a ctypes binding under that boundary calls; every comment names
+ * the reference function whose work the entry point does.
+ *
+ * Conventions: every pointer is a DEVICE pointer unless the name ends in `_host`; the caller
+ * owns every buffer (nothing is allocated here unless stated); `stream` is a cudaStream_t
+ * passed as void*; calls enqueue work and return without synchronising; the return value is
+ * NV41_OK or a negative NV41_ERR_* code; nothing throws.  Kernels that wait on barriers report
+ * a timed-out wait through a caller-provided 32-bit device `status` word (0 = ok) instead of
+ * hanging; read it with nv41_status_read after synchronising.
+ *
+ * Shapes: T tokens, k slots per token, R = T*k routed rows, E experts, D = model dim,
+ * I = expert intermediate dim.  "Padded row space": rows ordered expert-major (stable), each
+ * expert segment rounded up to 128 rows; P_max = ((R + E*128) / 128) * 128 rows are allocated
+ * (nanov41/triton_grouped_moe.py:473-474 with BM = 128).  FP8 buffers have their K extent
+ * rounded up to a multiple of 128 (zero codes in the padding).
+ */
+#ifndef NANOV41_B200_H_
+#define NANOV41_B200_H_
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define NV41_OK 0
+#define NV41_ERR_INVALID (-1)     /* bad pointer / size / alignment */
+#define NV41_ERR_CUDA (-2)        /* launch or driver error */
+#define NV41_ERR_UNSUPPORTED (-3) /* shape outside what the kernels implement */
+#define NV41_ERR_TIMEOUT (-4)     /* a device-side bounded wait ran out */
+
+/* Library / build identification: returns 100 * major + minor of this ABI. */
+int nv41_abi_version(void);
+
+/* Reads a device status word written by the GEMM kernels.  Synchronises `stream`.
+ * Returns NV41_OK, NV41_ERR_TIMEOUT (and *raw_host = the word) or NV41_ERR_CUDA. */
+int nv41_status_read(const unsigned* status, unsigned* raw_host, void* stream);
+
+/* ---- quantizers -------------------------------------------------------------------------- */
+
+/* FP8-e4m3 1x128 activation quantizer; arithmetic of ref/kernel.py:40-95,98-124 (act_quant,
+ * block 128, scale_fmt=None): s = max(amax, 1e-4) * fl32(1/448), code = e4m3_rn(clamp(x/s)).
+ * x: bf16 [*, ld_x]; output row r reads source row gather_rows[r] (or r when NULL; -1 = zeros).
+ * codes: u8 [rows, Kpad], Kpad = ceil(K/128)*128.  scales[r*stride_row + kb*stride_kb] fp32.
+ * K % 8 == 0.  (The reference asserts K % 128 == 0; a short last block is quantised as if
+ * zero-padded, which leaves amax, scale and the real codes unchanged.) */
+int nv41_quant_fp8_1x128(const void* x_bf16, long long ld_x, const int* gather_rows,
+                         long long rows, int K, void* codes, float* scales,
+                         long long scale_stride_row, long long scale_stride_kb, void* stream);
+
+/* FP8-e4m3 128x128 weight quantizer.  The reference has no 128x128 quantizer (weights arrive
+ * pre-quantised; layout consumed by ref/kernel.py:232,259-264, dequantised by
+ * ref/convert.py:159-172; the Triton FP8 path quantises per tensor,
+ * nanov41/triton_grouped_moe.py:918-944); the arithmetic is act_quant's over 128x128 blocks.
+ * w: bf16 [E, N, K] contiguous.  codes: u8 [E*N, Kpad].  scales: fp32 [E, ceil(N/128), Kpad/128].
+ * codes_t (optional): transposed copy u8 [E*Kpad, Npad], Npad = ceil(N/128)*128, zero padded. */
+int nv41_quant_fp8_128x128(const void* w_bf16, int E, int N, int K, void* codes, void* codes_t,
+                           float* scales, void* stream);
+
+/* NVFP4-e2m1 1x16 quantizer; experiments/tl_kernels/nvfp4_gemm.py:97-126 (quantize_nvfp4)
+ * applied to x / global_scale (global_scale = 1 reproduces the reference, which has no
+ * per-tensor scale).  x: bf16 or fp32 [rows, K] contiguous, K % 16 == 0.
+ * packed: u8 [rows, K/2] (low nibble = even column).  scale_bytes: e4m3 [rows, K/16] in
+ * plain row-major order (the reference additionally swizzles the words for sm_120). */
+int nv41_quant_nvfp4_1x16(const void* x, int x_is_fp32, long long rows, int K,
+                          float global_scale, void* packed, void* scale_bytes, void* stream);
+
+/* ---- router-sorted layout ---------------------------------------------------------------- */
+
+/* Bytes of scratch nv41_moe_layout_build needs. */
+long long nv41_moe_layout_workspace_bytes(long long R, int E);
+
+/* Stable expert-major ordering + 128-row padded layout; nanov41/fast_moe.py:289-308
+ * (_count_experts, _sort_tokens) and nanov41/triton_grouped_moe.py:455-538 (MoELayout).
+ * expert_idx: int64 (idx_is_i64 != 0) or int32 [R].  weights_flat: fp32 [R] or NULL.
+ * Outputs (int32): counts[E], cum_excl[E+1], pad_off[E+1], order[R], pad_pos[R],
+ * row_of_flat[R], flat_of_row[P_max] (-1 = padding), row_token[P_max] (-1 = padding),
+ * row_weight[P_max] fp32 (0 = padding; may be NULL), tile_expert[P_max/128] (-1 = unused),
+ * meta[4] = {used tiles, used padded rows, R, E}; *status = 1 if an index was out of range. */
+int nv41_moe_layout_build(const void* expert_idx, int idx_is_i64, const float* weights_flat,
+                          long long R, int E, int k, long long P_max, void* workspace,
+                          int* counts, int* cum_excl, int* pad_off, int* order, int* pad_pos,
+                          int* row_of_flat, int* flat_of_row, int* row_token, float* row_weight,
+                          int* tile_expert, int* meta, int* status, void* stream);
+
+/* Un-permute + top-k sum (+ shared expert) with fp32 accumulation and one bf16 rounding;
+ * nanov41/fast_moe.py:311-338,467-474 (_scatter_topk + shared add),
+ * nanov41/triton_grouped_moe.py:1193-1207 (_moe_tail_fwd_kernel).
+ * y_rows: bf16 [P_max, D]; shared: bf16 [T, D] or NULL; out: bf16 [T, D]; D % 8 == 0. */
+int nv41_moe_combine(const void* y_rows_bf16, const int* row_of_flat, const void* shared_bf16,
+                     void* out_bf16, long long T, int k, int D, void* stream);
+
+/* ---- grouped FP8 GEMMs (tcgen05 / TMEM) --------------------------------------------------- */
+
+/* a_mode values */
+#define NV41_A_CONTIGUOUS 0 /* a_src = e4m3 codes [a_rows = P_max, K] in the padded row space */
+#define NV41_A_GATHER_FP8 1 /* a_src = e4m3 codes [T, a_ld]; rows fetched through row_token   */
+
+/* Gate/up grouped GEMM + SwiGLU epilogue + 1x128 re-quantisation of h;
+ * nanov41/triton_grouped_moe.py:947-1043 (_swiglu_fwd[_nopad]_fp8_kernel),
+ * nanov41/fast_moe.py:341-350,404-409, nanov41/_ref_patched_model.py:858-868 (Expert.forward).
+ * gu = A @ [W1_e; W3_e]^T promoted per 128-wide K block with sa[row]*sw[n-block] (fp32),
+ * rounded to bf16; h = bf16(w_row * silu(min(gate, L)) * clamp(up, -L, L)); h is written as
+ * e4m3 codes [P_max, I] + scales [I/128][P_max].
+ * a_scale[kb * a_scale_kb_stride + (row | token)].  w13_codes: u8 [E, 2I, K] (gate rows then
+ * up rows); w13_scale: fp32 [E, 2I/128, K/128].  K % 128 == 0, I % 128 == 0.
+ * gate_out / up_out (both or neither) and h_out: optional bf16 [P_max, I]. */
+int nv41_moe_gemm1_fp8(int a_mode, const void* a_src, long long a_ld, int a_k_valid,
+                       const float* a_scale, long long a_scale_kb_stride, long long a_rows,
+                       const void* w13_codes, const float* w13_scale, int E, int I, int K,
+                       const int* tile_expert, const int* row_token, const float* row_weight,
+                       long long P_max, float swiglu_limit, void* h_codes, float* h_scale,
+                       void* gate_out, void* up_out, void* h_out, unsigned* status,
+                       void* stream);
+
+/* Plain grouped GEMM C[rows of expert e] = A @ B_e^T, bf16 out; the down projection and the
+ * dX GEMMs: nanov41/triton_grouped_moe.py:1046-1093 (_aggemm[_tb]_fp8_kernel),
+ * nanov41/fast_moe.py:409.  b_codes: u8 [E*N, K]; b_scale[e*bs_e + (n/128)*bs_nb + kb*bs_kb].
+ * c_out: bf16 [P_max, c_ld].  K % 128 == 0, N % 8 == 0. */
+int nv41_moe_gemm_fp8(int a_mode, const void* a_src, long long a_ld, const float* a_scale,
+                      long long a_scale_kb_stride, long long a_rows, const void* b_codes,
+                      const float* b_scale, long long bs_e, long long bs_nb, long long bs_kb,
+                      int E, int N, int K, const int* tile_expert, const int* row_token,
+                      long long P_max, void* c_out, long long c_ld, unsigned* status,
+                      void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* NANOV41_B200_H_ */

@@ -1,0 +1,61 @@
+"""ctypes binding of libnanov41_b200.so (the C-ABI CUDA library built by nanov41_b200.build).
+
+There is no fallback: if the library is missing, loading raises and every operator of this
+package fails loudly.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+LIB_PATH = Path(__file__).resolve().parent / "csrc" / "libnanov41_b200.so"
+
+OK, ERR_INVALID, ERR_CUDA, ERR_UNSUPPORTED, ERR_TIMEOUT = 0, -1, -2, -3, -4
+_ERR_NAMES = {ERR_INVALID: "invalid argument", ERR_CUDA: "CUDA launch/driver error",
+              ERR_UNSUPPORTED: "unsupported shape", ERR_TIMEOUT: "device-side wait timed out"}
+
+_p, _i, _ll, _f = C.c_void_p, C.c_int, C.c_longlong, C.c_float
+
+# name -> (restype, argtypes); mirrors include/nanov41_b200.h declaration by declaration
+SIGNATURES = {
+    "nv41_abi_version": (_i, []),
+    "nv41_status_read": (_i, [_p, _p, _p]),
+    "nv41_quant_fp8_1x128": (_i, [_p, _ll, _p, _ll, _i, _p, _p, _ll, _ll, _p]),
+    "nv41_quant_fp8_128x128": (_i, [_p, _i, _i, _i, _p, _p, _p, _p]),
+    "nv41_quant_nvfp4_1x16": (_i, [_p, _i, _ll, _i, _f, _p, _p, _p]),
+    "nv41_moe_layout_workspace_bytes": (_ll, [_ll, _i]),
+    "nv41_moe_layout_build": (_i, [_p, _i, _p, _ll, _i, _i, _ll, _p, _p, _p, _p, _p, _p, _p,
+                                   _p, _p, _p, _p, _p, _p, _p]),
+    "nv41_moe_combine": (_i, [_p, _p, _p, _p, _ll, _i, _i, _p]),
+    "nv41_moe_gemm1_fp8": (_i, [_i, _p, _ll, _i, _p, _ll, _ll, _p, _p, _i, _i, _i, _p, _p, _p,
+                                _ll, _f, _p, _p, _p, _p, _p, _p, _p]),
+    "nv41_moe_gemm_fp8": (_i, [_i, _p, _ll, _p, _ll, _ll, _p, _p, _ll, _ll, _ll, _i, _i, _i,
+                               _p, _p, _ll, _p, _ll, _p, _p]),
+}
+
+_lib = None
+
+
+class Nv41Error(RuntimeError):
+    pass
+
+
+def load():
+    """Load the shared library once and attach the prototypes."""
+    global _lib
+    if _lib is None:
+        if not LIB_PATH.exists():
+            raise Nv41Error(
+                f"{LIB_PATH} is missing: build it with `python -m nanov41_b200.build` "
+                "(this package has no CPU or PyTorch fallback)")
+        lib = C.CDLL(str(LIB_PATH))
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(lib, name)     # AttributeError if the symbol is not exported
+            fn.restype, fn.argtypes = res, args
+        _lib = lib
+    return _lib
+
+
+def check(rc: int, what: str) -> None:
+    if rc != OK:
+        raise Nv41Error(f"{what} failed: {_ERR_NAMES.get(rc, rc)} ({rc})")

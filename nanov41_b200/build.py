@@ -1,0 +1,62 @@
+"""Builds libnanov41_b200.so (the C-ABI CUDA library) in-tree with nvcc for sm_100a.
+
+Run as ``python -m nanov41_b200.build``.  nvcc cross-compiles without a GPU.  The library
+links the CUDA runtime statically and resolves the one driver entry point it needs
+(cuTensorMapEncodeTiled) at run time, so it loads on a machine without a driver.
+"""
+from __future__ import annotations
+
+import os
+import subprocess
+import sys
+from concurrent.futures import ThreadPoolExecutor
+from pathlib import Path
+
+CSRC = Path(__file__).resolve().parent / "csrc"
+LIB = CSRC / "libnanov41_b200.so"
+SOURCES = ["api.cu", "quant.cu", "layout.cu", "gemm_fp8.cu"]
+NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
+FLAGS = [
+    "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+    "-Xcompiler", "-fPIC", "-Xptxas", "-v",
+]
+
+
+def _stale(obj: Path, src: Path) -> bool:
+    if not obj.exists():
+        return True
+    newest = max(p.stat().st_mtime for p in list(CSRC.glob("*.cuh")) + [src] +
+                 [CSRC.parent.parent / "include" / "nanov41_b200.h"])
+    return obj.stat().st_mtime < newest
+
+
+def _compile(name: str, verbose: bool) -> str:
+    src, obj = CSRC / name, CSRC / (name[:-3] + ".o")
+    if not _stale(obj, src):
+        return ""
+    cmd = [NVCC, *FLAGS, "-c", str(src), "-o", str(obj)]
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if res.returncode != 0:
+        raise RuntimeError(f"nvcc failed for {name}:\n{res.stdout}\n{res.stderr}")
+    return res.stderr if verbose else ""
+
+
+def build(force: bool = False, verbose: bool = False) -> Path:
+    if force:
+        for name in SOURCES:
+            (CSRC / (name[:-3] + ".o")).unlink(missing_ok=True)
+    with ThreadPoolExecutor(max_workers=len(SOURCES)) as ex:
+        logs = list(ex.map(lambda n: _compile(n, verbose), SOURCES))
+    objs = [CSRC / (n[:-3] + ".o") for n in SOURCES]
+    if force or not LIB.exists() or any(o.stat().st_mtime > LIB.stat().st_mtime for o in objs):
+        cmd = [NVCC, "-shared", "-o", str(LIB), *map(str, objs), "-cudart", "static"]
+        res = subprocess.run(cmd, capture_output=True, text=True)
+        if res.returncode != 0:
+            raise RuntimeError(f"link failed:\n{res.stdout}\n{res.stderr}")
+    if verbose:
+        print("\n".join(l for l in logs if l))
+    return LIB
+
+
+if __name__ == "__main__":
+    print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))

@@ -1,0 +1,17 @@
+// Library identification and the device status word reader of the C ABI.
+#include <cuda_runtime.h>
+
+#include "../../include/nanov41_b200.h"
+
+extern "C" int nv41_abi_version(void) { return 100; }
+
+extern "C" int nv41_status_read(const unsigned* status, unsigned* raw_host, void* stream) {
+  if (!status) return NV41_ERR_INVALID;
+  unsigned v = 0;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (cudaMemcpyAsync(&v, status, sizeof(v), cudaMemcpyDeviceToHost, st) != cudaSuccess)
+    return NV41_ERR_CUDA;
+  if (cudaStreamSynchronize(st) != cudaSuccess) return NV41_ERR_CUDA;
+  if (raw_host) *raw_host = v;
+  return v == 0u ? NV41_OK : NV41_ERR_TIMEOUT;
+}

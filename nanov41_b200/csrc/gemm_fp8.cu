@@ -1,0 +1,602 @@
+// Grouped block-scaled FP8 expert GEMMs for sm_100a: TMA-fed tcgen05 (UMMA, kind::f8f6f4)
+// with TMEM accumulators, one persistent warp-specialised CTA per SM.
+//
+// What it replaces in the reference: the gate/up GEMM pair + SwiGLU epilogue
+// (nanov41/triton_grouped_moe.py:947-1043 _swiglu_fwd[_nopad]_fp8_kernel; torch path
+// nanov41/fast_moe.py:404-409), the down / dX grouped GEMMs (triton_grouped_moe.py:1046-1093
+// _aggemm[_tb]_fp8_kernel) with the scale semantics of ref/kernel.py:207-274 (fp8_gemm:
+// 1x128 activation scales, 128x128 weight scales, fp32 promotion of every 128-wide K block).
+//
+// Row space: the padded expert-major layout of MoELayout (every expert segment rounded up to
+// 128 rows), so an M tile never straddles two experts and tile t covers padded rows
+// [128 t, 128 t + 128).
+//
+// Pipeline per CTA (512 threads):
+//   warp 0      TMA producer: weight tiles (and activation tiles when they are contiguous)
+//   warp 1      UMMA issuer (one thread) + TMEM allocation
+//   warps 4-7   activation producers for the gathered modes: fetch the rows of the tile by
+//               token index (fp8 codes, or bf16 rows that are quantised 1x128 on the fly) and
+//               write them into the 128-byte-swizzled stage
+//   warps 8-15  promotion + epilogue: every 128-wide K block is read back from TMEM
+//               (tcgen05.ld) and folded into fp32 registers with sa[row] * sw[n-block]
+//               (the scales are arbitrary fp32, so the hardware block-scaled kinds, which take
+//               power-of-two ue8m0 scales, do not apply), then SwiGLU + re-quantisation or a
+//               bf16 store.
+// TMEM holds two 256-column accumulator buffers, so the UMMAs of K block i+1 overlap the
+// promotion of K block i.  Every mbarrier wait is bounded and reports through `status`.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp8.h>
+#include <cstdint>
+#include <cstring>
+
+#include "../../include/nanov41_b200.h"
+#include "ptx.cuh"
+#include "util.cuh"
+
+namespace nv41 {
+
+constexpr int kBM = 128;                 // tile rows
+constexpr int kBK = 128;                 // K per stage = one scale block = one swizzle row
+constexpr int kBN = 256;                 // UMMA N (two 128-row weight boxes)
+constexpr int kStages = 4;
+constexpr int kABytes = kBM * kBK;       // 16 KiB
+constexpr int kBBytes = kBN * kBK;       // 32 KiB
+constexpr int kStageBytes = kABytes + kBBytes;
+constexpr int kThreads = 512;
+constexpr int kTmemCols = 512;
+
+enum { A_TMA = 0, A_GATHER_FP8 = 1, A_GATHER_QUANT = 2 };
+enum { EPI_SWIGLU = 0, EPI_STORE = 1 };
+
+struct GemmArgs {
+  CUtensorMap tmap_a;
+  CUtensorMap tmap_b;
+  const uint8_t* a_codes;        // A_GATHER_FP8: [T, K] e4m3
+  const __nv_bfloat16* a_bf16;   // A_GATHER_QUANT: [T, ld] bf16
+  long long a_ld;                // row stride (elements) of the gathered source
+  int a_k_valid;                 // A_GATHER_QUANT: real K of the bf16 rows (<= K)
+  const float* a_scale;          // [K/128][rows or tokens], k-block major
+  long long a_scale_kb_stride;
+  const float* b_scale;          // b_scale[e*bs_e + nb*bs_nb + kb*bs_kb]
+  long long bs_e, bs_nb, bs_kb;
+  int b_scale_nnb;               // number of valid n-blocks per expert
+  const int* tile_expert;        // [n_tiles_m]
+  const int* row_token;          // [P_max] (-1 = padding row)
+  const float* row_weight;       // [P_max]
+  int n_tiles_m, n_tiles_n, nkb;
+  int b_rows_per_expert;         // rows of one expert in the weight tensor map
+  int b_up_row_offset;           // EPI_SWIGLU: first up-projection row inside the expert
+  int N;                         // valid output columns
+  float limit;
+  uint8_t* h_codes;              // EPI_SWIGLU: [P_max, h_ld] e4m3
+  long long h_ld;
+  float* h_scale;                // [N/128][P_max]
+  long long h_scale_nb_stride;
+  __nv_bfloat16* gate_out;       // optional [P_max, N] (saved for backward)
+  __nv_bfloat16* up_out;
+  __nv_bfloat16* h_out;          // optional bf16 copy of h
+  __nv_bfloat16* c_out;          // EPI_STORE: [P_max, c_ld]
+  long long c_ld;
+  uint32_t* status;
+};
+
+struct Smem {
+  uint8_t* base;
+  __device__ uint8_t* a(int s) const { return base + s * kStageBytes; }
+  __device__ uint8_t* b(int s) const { return base + s * kStageBytes + kABytes; }
+  __device__ uint64_t* bars() const {
+    return reinterpret_cast<uint64_t*>(base + kStages * kStageBytes);
+  }
+  __device__ uint64_t* full(int s) const { return bars() + s; }
+  __device__ uint64_t* empty(int s) const { return bars() + kStages + s; }
+  __device__ uint64_t* tfull(int b) const { return bars() + 2 * kStages + b; }
+  __device__ uint64_t* tempty(int b) const { return bars() + 2 * kStages + 2 + b; }
+  __device__ uint64_t* xbar(int b) const { return bars() + 2 * kStages + 4 + b; }
+  __device__ uint32_t* tmem_slot() const {
+    return reinterpret_cast<uint32_t*>(bars() + 2 * kStages + 6);
+  }
+  __device__ volatile uint32_t* abort_flag() const { return tmem_slot() + 1; }
+  __device__ float* xch() const { return reinterpret_cast<float*>(tmem_slot() + 4); }  // [2][2][128]
+};
+constexpr int kSmemTail = (2 * kStages + 6) * 8 + 16 + 2 * 2 * 128 * 4;
+constexpr int kSmemBytes = kStages * kStageBytes + kSmemTail + 1024;  // +1024: manual alignment
+
+__device__ __forceinline__ float bf16_round(float x) {
+  return __bfloat162float(__float2bfloat16_rn(x));
+}
+__device__ __forceinline__ uint32_t pack_bf16x2(float a, float b) {
+  const __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
+__device__ __forceinline__ uint32_t e4m3x4(float a, float b, float c, float d, float s) {
+  const float q0 = fminf(fmaxf(__fdiv_rn(a, s), -448.f), 448.f);
+  const float q1 = fminf(fmaxf(__fdiv_rn(b, s), -448.f), 448.f);
+  const float q2 = fminf(fmaxf(__fdiv_rn(c, s), -448.f), 448.f);
+  const float q3 = fminf(fmaxf(__fdiv_rn(d, s), -448.f), 448.f);
+  const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(q0, q1), __NV_SATFINITE, __NV_E4M3);
+  const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(q2, q3), __NV_SATFINITE, __NV_E4M3);
+  return lo | (hi << 16);
+}
+
+// ------------------------------------------------------------------------------ TMA warp
+template <int MODE_A, int EPI>
+__device__ __forceinline__ void role_tma(const GemmArgs& g, const Smem& sm) {
+  uint32_t it = 0;
+  const int total = g.n_tiles_m * g.n_tiles_n;
+  for (int w = blockIdx.x; w < total; w += gridDim.x) {
+    const int mt = w / g.n_tiles_n, nt = w - mt * g.n_tiles_n;
+    const int e = g.tile_expert[mt];
+    if (e < 0) continue;
+    int brow0, brow1;
+    if (EPI == EPI_SWIGLU) {
+      brow0 = e * g.b_rows_per_expert + nt * 128;
+      brow1 = brow0 + g.b_up_row_offset;
+    } else {
+      brow0 = e * g.b_rows_per_expert + nt * kBN;
+      brow1 = brow0 + 128;
+    }
+    for (int kb = 0; kb < g.nkb; ++kb, ++it) {
+      const int s = it % kStages;
+      const uint32_t ph = (it / kStages) & 1u;
+      if (!mbar_wait(sm.empty(s), ph ^ 1u, sm.abort_flag(), g.status, ST_TIMEOUT_EMPTY)) return;
+      const uint32_t bytes = kBBytes + (MODE_A == A_TMA ? kABytes : 0);
+      mbar_arrive_expect_tx(sm.full(s), bytes);
+      if (MODE_A == A_TMA) tma_load_2d(sm.a(s), &g.tmap_a, kb * kBK, mt * kBM, sm.full(s));
+      tma_load_2d(sm.b(s), &g.tmap_b, kb * kBK, brow0, sm.full(s));
+      tma_load_2d(sm.b(s) + 128 * kBK, &g.tmap_b, kb * kBK, brow1, sm.full(s));
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------ UMMA warp
+__device__ __forceinline__ void role_mma(const GemmArgs& g, const Smem& sm, uint32_t tmem_base) {
+  constexpr uint32_t idesc = umma_idesc(kBM, kBN, 0, 0);
+  uint32_t it = 0;
+  const int total = g.n_tiles_m * g.n_tiles_n;
+  for (int w = blockIdx.x; w < total; w += gridDim.x) {
+    const int mt = w / g.n_tiles_n;
+    if (g.tile_expert[mt] < 0) continue;
+    for (int kb = 0; kb < g.nkb; ++kb, ++it) {
+      const int s = it % kStages;
+      const uint32_t ph = (it / kStages) & 1u;
+      const uint32_t b = it & 1u, tph = (it >> 1) & 1u;
+      if (!mbar_wait(sm.full(s), ph, sm.abort_flag(), g.status, ST_TIMEOUT_FULL)) return;
+      if (!mbar_wait(sm.tempty(b), tph ^ 1u, sm.abort_flag(), g.status, ST_TIMEOUT_TMEM_EMPTY))
+        return;
+      tc_fence_after_sync();
+      const uint64_t adesc = umma_desc_kmajor_sw128(smem_u32(sm.a(s)));
+      const uint64_t bdesc = umma_desc_kmajor_sw128(smem_u32(sm.b(s)));
+      const uint32_t d = tmem_base + b * kBN;
+#pragma unroll
+      for (int j = 0; j < kBK / 32; ++j)     // UMMA K = 32 bytes; +2 = 32 B in 16-byte units
+        umma_f8f6f4(d, adesc + 2 * j, bdesc + 2 * j, idesc, j > 0 ? 1u : 0u);
+      umma_commit(sm.empty(s));              // smem stage free once these UMMAs have read it
+      umma_commit(sm.tfull(b));              // accumulator buffer ready for promotion
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------ A producers
+// 4 warps; lane -> 16-byte chunk (lane & 7) of rows (lane >> 3) + 4 i of the warp's 32 rows.
+template <int MODE_A>
+__device__ __forceinline__ void role_gather(const GemmArgs& g, const Smem& sm, int pw, int lane) {
+  uint32_t it = 0;
+  const int total = g.n_tiles_m * g.n_tiles_n;
+  const int c = lane & 7;
+  for (int w = blockIdx.x; w < total; w += gridDim.x) {
+    const int mt = w / g.n_tiles_n;
+    if (g.tile_expert[mt] < 0) continue;
+    int tok[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) tok[i] = g.row_token[mt * kBM + pw * 32 + i * 4 + (lane >> 3)];
+    for (int kb = 0; kb < g.nkb; ++kb, ++it) {
+      const int s = it % kStages;
+      const uint32_t ph = (it / kStages) & 1u;
+      if (!mbar_wait(sm.empty(s), ph ^ 1u, sm.abort_flag(), g.status, ST_TIMEOUT_EMPTY)) return;
+      uint8_t* dst = sm.a(s);
+      if (MODE_A == A_GATHER_FP8) {
+        uint4 v[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          v[i] = make_uint4(0u, 0u, 0u, 0u);
+          if (tok[i] >= 0)
+            v[i] = __ldg(reinterpret_cast<const uint4*>(g.a_codes + tok[i] * g.a_ld + kb * kBK +
+                                                        c * 16));
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int r = pw * 32 + i * 4 + (lane >> 3);
+          *reinterpret_cast<uint4*>(dst + r * 128 + ((c ^ (r & 7)) << 4)) = v[i];
+        }
+      }
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(sm.full(s));
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------ epilogue
+template <int MODE_A, int EPI>
+__device__ __forceinline__ void role_epilogue(const GemmArgs& g, const Smem& sm,
+                                              uint32_t tmem_base, int ew, int lane) {
+  const int q = ew & 3;            // TMEM lane quarter this warp may read
+  const int half = ew >> 2;        // which half of the tile's columns
+  const int row_in_tile = q * 32 + lane;
+  const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
+  uint32_t it = 0, unit = 0;
+  const int total = g.n_tiles_m * g.n_tiles_n;
+  for (int w = blockIdx.x; w < total; w += gridDim.x) {
+    const int mt = w / g.n_tiles_n, nt = w - mt * g.n_tiles_n;
+    const int e = g.tile_expert[mt];
+    if (e < 0) continue;
+    const long long grow = static_cast<long long>(mt) * kBM + row_in_tile;
+    long long sa_idx = grow;
+    bool sa_ok = true;
+    if (MODE_A != A_TMA) {
+      const int tok = g.row_token[grow];
+      sa_ok = tok >= 0;
+      sa_idx = sa_ok ? tok : 0;
+    }
+    int nb0, nb1;
+    if (EPI == EPI_SWIGLU) {
+      nb0 = nt;
+      nb1 = g.b_up_row_offset / 128 + nt;
+    } else {
+      nb0 = nb1 = nt * 2 + half;
+    }
+    const bool nb_ok = nb0 < g.b_scale_nnb && nb1 < g.b_scale_nnb;
+    const float* sb0 = g.b_scale + e * g.bs_e + (nb_ok ? nb0 : 0) * g.bs_nb;
+    const float* sb1 = g.b_scale + e * g.bs_e + (nb_ok ? nb1 : 0) * g.bs_nb;
+
+    float acc[128];
+#pragma unroll
+    for (int i = 0; i < 128; ++i) acc[i] = 0.f;
+
+    float sa_n = sa_ok ? __ldg(g.a_scale + sa_idx) : 0.f;
+    float s0_n = __ldg(sb0), s1_n = __ldg(sb1);
+    for (int kb = 0; kb < g.nkb; ++kb, ++it) {
+      const uint32_t b = it & 1u, tph = (it >> 1) & 1u;
+      const float f0 = sa_n * s0_n, f1 = sa_n * s1_n;
+      if (kb + 1 < g.nkb) {   // prefetch the next block's scales behind the barrier wait
+        sa_n = sa_ok ? __ldg(g.a_scale + (kb + 1) * g.a_scale_kb_stride + sa_idx) : 0.f;
+        s0_n = __ldg(sb0 + (kb + 1) * g.bs_kb);
+        s1_n = __ldg(sb1 + (kb + 1) * g.bs_kb);
+      }
+      if (!mbar_wait(sm.tfull(b), tph, sm.abort_flag(), g.status, ST_TIMEOUT_TMEM_FULL)) return;
+      tc_fence_after_sync();
+      const uint32_t tb = lane_base + b * kBN;
+#pragma unroll
+      for (int ch = 0; ch < 4; ++ch) {
+        // EPI_SWIGLU: chunks 0,1 = gate columns half*64 + {0,32}; 2,3 = up columns (+128)
+        // EPI_STORE : chunks 0..3 = columns half*128 + 32*ch
+        const int col = (EPI == EPI_SWIGLU) ? ((ch >> 1) * 128 + half * 64 + (ch & 1) * 32)
+                                            : (half * 128 + ch * 32);
+        const float f = (EPI == EPI_SWIGLU) ? ((ch >> 1) ? f1 : f0) : f0;
+        uint32_t v[32];
+        tmem_ld_32x32b_x32(tb + col, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+          acc[ch * 32 + i] = fmaf(__uint_as_float(v[i]), f, acc[ch * 32 + i]);
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(sm.tempty(b));
+    }
+
+    if (EPI == EPI_SWIGLU) {
+      // acc[0..63] = gate, acc[64..127] = up for h columns nt*128 + half*64 + i
+      const float wr = g.row_weight[grow];
+      const float L = g.limit;
+      const long long ocol = static_cast<long long>(nt) * 128 + half * 64;
+      if (g.gate_out) {
+#pragma unroll
+        for (int i = 0; i < 64; i += 8) {
+          uint4 vg, vu;
+          vg.x = pack_bf16x2(acc[i], acc[i + 1]);     vg.y = pack_bf16x2(acc[i + 2], acc[i + 3]);
+          vg.z = pack_bf16x2(acc[i + 4], acc[i + 5]); vg.w = pack_bf16x2(acc[i + 6], acc[i + 7]);
+          vu.x = pack_bf16x2(acc[64 + i], acc[65 + i]); vu.y = pack_bf16x2(acc[66 + i], acc[67 + i]);
+          vu.z = pack_bf16x2(acc[68 + i], acc[69 + i]); vu.w = pack_bf16x2(acc[70 + i], acc[71 + i]);
+          *reinterpret_cast<uint4*>(g.gate_out + grow * g.N + ocol + i) = vg;
+          *reinterpret_cast<uint4*>(g.up_out + grow * g.N + ocol + i) = vu;
+        }
+      }
+      float amax = 0.f;
+#pragma unroll
+      for (int i = 0; i < 64; ++i) {
+        float gt = bf16_round(acc[i]);          // Linear output is bf16, then .float()
+        float up = bf16_round(acc[64 + i]);
+        if (L > 0.f) {
+          up = fminf(fmaxf(up, -L), L);
+          gt = fminf(gt, L);
+        }
+        const float sl = __fdividef(gt, 1.f + __expf(-gt));
+        const float hv = bf16_round((sl * up) * wr);
+        acc[i] = hv;
+        amax = fmaxf(amax, fabsf(hv));
+      }
+      if (g.h_out) {
+#pragma unroll
+        for (int i = 0; i < 64; i += 8) {
+          uint4 vh;
+          vh.x = pack_bf16x2(acc[i], acc[i + 1]);     vh.y = pack_bf16x2(acc[i + 2], acc[i + 3]);
+          vh.z = pack_bf16x2(acc[i + 4], acc[i + 5]); vh.w = pack_bf16x2(acc[i + 6], acc[i + 7]);
+          *reinterpret_cast<uint4*>(g.h_out + grow * g.N + ocol + i) = vh;
+        }
+      }
+      // the 1x128 block of h spans both column halves: exchange the partial maxima
+      float* x = sm.xch() + (unit & 1u) * 256;
+      x[half * 128 + row_in_tile] = amax;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(sm.xbar(unit & 1u));
+      if (!mbar_wait(sm.xbar(unit & 1u), (unit >> 1) & 1u, sm.abort_flag(), g.status,
+                     ST_TIMEOUT_AUX))
+        return;
+      amax = fmaxf(x[row_in_tile], x[128 + row_in_tile]);
+      const float s = fmaxf(amax, 1e-4f) * (1.0f / 448.0f);
+      uint8_t* hp = g.h_codes + grow * g.h_ld + ocol;
+#pragma unroll
+      for (int i = 0; i < 64; i += 16) {
+        uint4 vc;
+        vc.x = e4m3x4(acc[i], acc[i + 1], acc[i + 2], acc[i + 3], s);
+        vc.y = e4m3x4(acc[i + 4], acc[i + 5], acc[i + 6], acc[i + 7], s);
+        vc.z = e4m3x4(acc[i + 8], acc[i + 9], acc[i + 10], acc[i + 11], s);
+        vc.w = e4m3x4(acc[i + 12], acc[i + 13], acc[i + 14], acc[i + 15], s);
+        *reinterpret_cast<uint4*>(hp + i) = vc;
+      }
+      if (half == 0) g.h_scale[nt * g.h_scale_nb_stride + grow] = s;
+    } else {
+      const long long ocol = static_cast<long long>(nt) * kBN + half * 128;
+      __nv_bfloat16* cp = g.c_out + grow * g.c_ld + ocol;
+#pragma unroll
+      for (int i = 0; i < 128; i += 8) {
+        if (ocol + i < g.N) {          // N % 8 == 0: a chunk is entirely valid or not
+          uint4 vc;
+          vc.x = pack_bf16x2(acc[i], acc[i + 1]);     vc.y = pack_bf16x2(acc[i + 2], acc[i + 3]);
+          vc.z = pack_bf16x2(acc[i + 4], acc[i + 5]); vc.w = pack_bf16x2(acc[i + 6], acc[i + 7]);
+          *reinterpret_cast<uint4*>(cp + i) = vc;
+        }
+      }
+    }
+    ++unit;
+  }
+}
+
+// ------------------------------------------------------------------------------ kernel
+template <int MODE_A, int EPI>
+__global__ void __launch_bounds__(kThreads, 1)
+grouped_gemm_fp8_kernel(const __grid_constant__ GemmArgs g) {
+  extern __shared__ uint8_t smem_raw[];
+  Smem sm;
+  sm.base = reinterpret_cast<uint8_t*>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    const uint32_t full_count = (MODE_A == A_TMA) ? 1u : 5u;   // TMA thread (+ 4 producer warps)
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(sm.full(s), full_count);
+      mbar_init(sm.empty(s), 1u);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(sm.tfull(b), 1u);
+      mbar_init(sm.tempty(b), 8u);      // one arrival per epilogue warp
+      mbar_init(sm.xbar(b), 8u);
+    }
+    *sm.abort_flag() = 0u;
+    fence_mbar_init();
+    tma_prefetch_desc(&g.tmap_b);
+    if (MODE_A == A_TMA) tma_prefetch_desc(&g.tmap_a);
+  }
+  if (warp == 1) {
+    tmem_alloc(sm.tmem_slot(), kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *sm.tmem_slot();
+
+  const int wg = warp >> 2;
+  if (wg == 0) {
+    setmaxnreg_dec<56>();
+    if (warp == 0) {
+      if (lane == 0) role_tma<MODE_A, EPI>(g, sm);
+    } else if (warp == 1) {
+      if (lane == 0) role_mma(g, sm, tmem_base);
+    }
+  } else if (wg == 1) {
+    setmaxnreg_dec<104>();
+    if (MODE_A != A_TMA) role_gather<MODE_A>(g, sm, warp - 4, lane);
+  } else {
+    setmaxnreg_inc<176>();
+    role_epilogue<MODE_A, EPI>(g, sm, tmem_base, warp - 8, lane);
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  if (*sm.abort_flag()) {
+    // give copies that may still be in flight time to land before the CTA's smem is released
+    for (int i = 0; i < 64; ++i) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) tmem_dealloc(tmem_base, kTmemCols);
+}
+
+// ------------------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) ==
+            cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+// 2-D u8 tensor [rows, cols] (cols contiguous), box 128 rows x 128 bytes, 128-byte swizzle.
+static int make_tmap_u8(CUtensorMap* m, const void* base, unsigned long long rows,
+                        unsigned long long cols) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return NV41_ERR_CUDA;
+  if ((reinterpret_cast<uintptr_t>(base) & 15u) || (cols % 16) != 0) return NV41_ERR_INVALID;
+  const cuuint64_t dims[2] = {cols, rows};
+  const cuuint64_t strides[1] = {cols};
+  const cuuint32_t box[2] = {128, 128};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims,
+                        strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? NV41_OK : NV41_ERR_CUDA;
+}
+
+static int sm_count() {
+  static int n = 0;
+  if (n == 0) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return 148;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
+      n = 148;
+  }
+  return n;
+}
+
+template <int MODE_A, int EPI>
+static int launch(const GemmArgs& a, cudaStream_t st) {
+  static bool configured = false;
+  auto kern = grouped_gemm_fp8_kernel<MODE_A, EPI>;
+  if (!configured) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) !=
+        cudaSuccess)
+      return NV41_ERR_CUDA;
+    configured = true;
+  }
+  long long units = static_cast<long long>(a.n_tiles_m) * a.n_tiles_n;
+  if (units <= 0) return NV41_OK;
+  int grid = sm_count();
+  if (units < grid) grid = static_cast<int>(units);
+  kern<<<grid, kThreads, kSmemBytes, st>>>(a);
+  return launch_status();
+}
+
+}  // namespace nv41
+
+using namespace nv41;
+
+extern "C" int nv41_moe_gemm1_fp8(int a_mode, const void* a_src, long long a_ld, int a_k_valid,
+                                  const float* a_scale, long long a_scale_kb_stride,
+                                  long long a_rows, const void* w13_codes, const float* w13_scale,
+                                  int E, int I, int K, const int* tile_expert,
+                                  const int* row_token, const float* row_weight, long long P_max,
+                                  float swiglu_limit, void* h_codes, float* h_scale,
+                                  void* gate_out, void* up_out, void* h_out, unsigned* status,
+                                  void* stream) {
+  if (!a_src || !w13_codes || !w13_scale || !tile_expert || !row_token || !row_weight ||
+      !h_codes || !h_scale || !status)
+    return NV41_ERR_INVALID;
+  if (E <= 0 || I <= 0 || K <= 0 || P_max <= 0 || (P_max % 128) != 0) return NV41_ERR_INVALID;
+  if ((K % 128) != 0 || (I % 128) != 0) return NV41_ERR_UNSUPPORTED;
+  if ((gate_out == nullptr) != (up_out == nullptr)) return NV41_ERR_INVALID;
+  if (a_mode != A_TMA && a_mode != A_GATHER_FP8) return NV41_ERR_UNSUPPORTED;
+  if (a_mode != A_GATHER_QUANT && !a_scale) return NV41_ERR_INVALID;
+  GemmArgs g;
+  memset(&g, 0, sizeof(g));
+  int rc = make_tmap_u8(&g.tmap_b, w13_codes, static_cast<unsigned long long>(E) * 2 * I, K);
+  if (rc != NV41_OK) return rc;
+  if (a_mode == A_TMA) {
+    rc = make_tmap_u8(&g.tmap_a, a_src, static_cast<unsigned long long>(a_rows), K);
+    if (rc != NV41_OK) return rc;
+  }
+  g.a_codes = static_cast<const uint8_t*>(a_src);
+  g.a_bf16 = static_cast<const __nv_bfloat16*>(a_src);
+  g.a_ld = a_ld;
+  g.a_k_valid = a_k_valid;
+  g.a_scale = a_scale;
+  g.a_scale_kb_stride = a_scale_kb_stride;
+  g.b_scale = w13_scale;
+  g.bs_kb = 1;
+  g.bs_nb = K / 128;
+  g.bs_e = static_cast<long long>(2 * I / 128) * (K / 128);
+  g.b_scale_nnb = 2 * I / 128;
+  g.tile_expert = tile_expert;
+  g.row_token = row_token;
+  g.row_weight = row_weight;
+  g.n_tiles_m = static_cast<int>(P_max / 128);
+  g.n_tiles_n = I / 128;
+  g.nkb = K / 128;
+  g.b_rows_per_expert = 2 * I;
+  g.b_up_row_offset = I;
+  g.N = I;
+  g.limit = swiglu_limit;
+  g.h_codes = static_cast<uint8_t*>(h_codes);
+  g.h_ld = I;
+  g.h_scale = h_scale;
+  g.h_scale_nb_stride = P_max;
+  g.gate_out = static_cast<__nv_bfloat16*>(gate_out);
+  g.up_out = static_cast<__nv_bfloat16*>(up_out);
+  g.h_out = static_cast<__nv_bfloat16*>(h_out);
+  g.status = status;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (a_mode == A_TMA) return launch<A_TMA, EPI_SWIGLU>(g, st);
+  return launch<A_GATHER_FP8, EPI_SWIGLU>(g, st);
+}
+
+extern "C" int nv41_moe_gemm_fp8(int a_mode, const void* a_src, long long a_ld,
+                                 const float* a_scale, long long a_scale_kb_stride,
+                                 long long a_rows, const void* b_codes, const float* b_scale,
+                                 long long bs_e, long long bs_nb, long long bs_kb, int E, int N,
+                                 int K, const int* tile_expert, const int* row_token,
+                                 long long P_max, void* c_out, long long c_ld, unsigned* status,
+                                 void* stream) {
+  if (!a_src || !a_scale || !b_codes || !b_scale || !tile_expert || !c_out || !status)
+    return NV41_ERR_INVALID;
+  if (E <= 0 || N <= 0 || K <= 0 || P_max <= 0 || (P_max % 128) != 0 || c_ld < N)
+    return NV41_ERR_INVALID;
+  if ((K % 128) != 0 || (N % 8) != 0 || (c_ld % 8) != 0) return NV41_ERR_UNSUPPORTED;
+  if (a_mode != A_TMA && a_mode != A_GATHER_FP8) return NV41_ERR_UNSUPPORTED;
+  if (a_mode == A_GATHER_FP8 && !row_token) return NV41_ERR_INVALID;
+  GemmArgs g;
+  memset(&g, 0, sizeof(g));
+  int rc = make_tmap_u8(&g.tmap_b, b_codes, static_cast<unsigned long long>(E) * N, K);
+  if (rc != NV41_OK) return rc;
+  if (a_mode == A_TMA) {
+    rc = make_tmap_u8(&g.tmap_a, a_src, static_cast<unsigned long long>(a_rows), K);
+    if (rc != NV41_OK) return rc;
+  }
+  g.a_codes = static_cast<const uint8_t*>(a_src);
+  g.a_ld = a_ld;
+  g.a_scale = a_scale;
+  g.a_scale_kb_stride = a_scale_kb_stride;
+  g.b_scale = b_scale;
+  g.bs_e = bs_e;
+  g.bs_nb = bs_nb;
+  g.bs_kb = bs_kb;
+  g.b_scale_nnb = (N + 127) / 128;
+  g.tile_expert = tile_expert;
+  g.row_token = row_token;
+  g.n_tiles_m = static_cast<int>(P_max / 128);
+  g.n_tiles_n = (N + kBN - 1) / kBN;
+  g.nkb = K / 128;
+  g.b_rows_per_expert = N;
+  g.N = N;
+  g.c_out = static_cast<__nv_bfloat16*>(c_out);
+  g.c_ld = c_ld;
+  g.status = status;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (a_mode == A_TMA) return launch<A_TMA, EPI_STORE>(g, st);
+  return launch<A_GATHER_FP8, EPI_STORE>(g, st);
+}

@@ -1,0 +1,276 @@
+// Router-sorted token layout and the un-permute/top-k combine of the MoE expert path.
+//
+// Layout (integer work, deterministic): the flat (token, slot) rows are ordered expert-major by a
+// STABLE counting sort, exactly the order torch.argsort(flat_expert, stable=True) gives in
+// nanov41/fast_moe.py:296-308 (_sort_tokens) and nanov41/triton_grouped_moe.py:455-538
+// (MoELayout); every expert's segment is then padded to a multiple of 128 rows
+// (pad_off / pad_pos / tile_e / row_of_flat / flat_of_row of MoELayout, with BM = 128).
+//
+// Three launches: per-warp histograms -> one-block scan -> stable scatter.  A warp owns a
+// contiguous run of 256 flat rows, so ranks inside the run follow flat order and runs are
+// ordered by the scan: the result does not depend on scheduling.
+//
+// Combine: out[t] = bf16( sum_j fp32(y[row_of_flat[t*k+j]]) + fp32(shared[t]) ), the fp32
+// accumulation and single rounding of nanov41/fast_moe.py:311-338,467-474.
+#include <cuda_bf16.h>
+#include <cstdint>
+
+#include "../../include/nanov41_b200.h"
+#include "util.cuh"
+
+namespace nv41 {
+
+constexpr int kRun = 256;        // flat rows per warp
+constexpr int kWarpsPerCta = 8;
+
+__device__ __forceinline__ int load_expert(const void* idx, int is_i64, long long f) {
+  return is_i64 ? static_cast<int>(reinterpret_cast<const long long*>(idx)[f])
+                : reinterpret_cast<const int*>(idx)[f];
+}
+
+// hist[run][e] = number of rows of expert e inside the run.  Also resets the per-row maps of
+// the padded space (padding rows keep token -1 / weight 0).
+__global__ void __launch_bounds__(kWarpsPerCta * 32)
+layout_hist_kernel(const void* __restrict__ idx, int is_i64, long long R, int E, int n_runs,
+                   int* __restrict__ hist, long long P_max, int* __restrict__ flat_of_row,
+                   int* __restrict__ row_token, float* __restrict__ row_weight,
+                   int* __restrict__ status) {
+  extern __shared__ int sh[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  int* my = sh + warp * E;
+  for (int e = lane; e < E; e += 32) my[e] = 0;
+  __syncwarp();
+  const int run = blockIdx.x * kWarpsPerCta + warp;
+  if (run < n_runs) {
+    const long long base = static_cast<long long>(run) * kRun;
+    for (int i = 0; i < kRun; i += 32) {
+      const long long f = base + i + lane;
+      const bool valid = f < R;
+      int e = valid ? load_expert(idx, is_i64, f) : -1;
+      if (valid && (e < 0 || e >= E)) {
+        atomicExch(status, 1);
+        e = e < 0 ? 0 : E - 1;
+      }
+      const unsigned peers = __match_any_sync(0xFFFFFFFFu, e);
+      if (valid && (peers & ((1u << lane) - 1u)) == 0u) my[e] += __popc(peers);
+      __syncwarp();
+    }
+    for (int e = lane; e < E; e += 32) hist[static_cast<long long>(run) * E + e] = my[e];
+  }
+  const long long gtid = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const long long gstride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long p = gtid; p < P_max; p += gstride) {
+    flat_of_row[p] = -1;
+    row_token[p] = -1;
+    if (row_weight) row_weight[p] = 0.f;
+  }
+}
+
+// One CTA.  Turns hist[run][e] into the sorted start of (run, e) and emits the per-expert
+// tables: counts, cum_excl (exclusive cumsum of counts, [E+1]), pad_off ([E+1], segments
+// rounded up to 128 rows), tile_expert ([n_tiles_max], -1 past the last used tile) and
+// meta = {used tiles, used padded rows, R, E}.
+__global__ void __launch_bounds__(1024)
+layout_scan_kernel(int* __restrict__ hist, int n_runs, int E, long long R, int n_tiles_max,
+                   int* __restrict__ counts, int* __restrict__ cum_excl,
+                   int* __restrict__ pad_off, int* __restrict__ tile_expert,
+                   int* __restrict__ meta) {
+  extern __shared__ int sh[];          // [E] totals, then [E+1] cum_excl, then [E+1] pad_off
+  int* tot = sh;
+  int* cum = sh + E;
+  int* pof = sh + 2 * E + 1;
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    int run_sum = 0;
+    for (int r = 0; r < n_runs; ++r) {
+      const long long o = static_cast<long long>(r) * E + e;
+      const int c = hist[o];
+      hist[o] = run_sum;               // exclusive prefix over runs, per expert
+      run_sum += c;
+    }
+    tot[e] = run_sum;
+    counts[e] = run_sum;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int c = 0, p = 0;
+    for (int e = 0; e < E; ++e) {
+      cum[e] = c;
+      pof[e] = p;
+      c += tot[e];
+      p += (tot[e] + 127) / 128 * 128;
+    }
+    cum[E] = c;
+    pof[E] = p;
+    meta[0] = p / 128;
+    meta[1] = p;
+    meta[2] = static_cast<int>(R);
+    meta[3] = E;
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e <= E; e += blockDim.x) {
+    cum_excl[e] = cum[e];
+    pad_off[e] = pof[e];
+  }
+  // add the expert's sorted start to every (run, e) prefix
+  for (long long o = threadIdx.x; o < static_cast<long long>(n_runs) * E; o += blockDim.x)
+    hist[o] += cum[o % E];
+  // tile -> expert table
+  for (int t = threadIdx.x; t < n_tiles_max; t += blockDim.x) {
+    const int row = t * 128;
+    int ex = -1;
+    if (row < pof[E]) {
+      int lo = 0, hi = E;              // last e with pof[e] <= row
+      while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (pof[mid] <= row) lo = mid; else hi = mid;
+      }
+      ex = lo;
+    }
+    tile_expert[t] = ex;
+  }
+}
+
+__global__ void __launch_bounds__(kWarpsPerCta * 32)
+layout_scatter_kernel(const void* __restrict__ idx, int is_i64,
+                      const float* __restrict__ weights_flat, long long R, int E, int k,
+                      int n_runs, const int* __restrict__ start, const int* __restrict__ cum_excl,
+                      const int* __restrict__ pad_off, int* __restrict__ order,
+                      int* __restrict__ pad_pos, int* __restrict__ row_of_flat,
+                      int* __restrict__ flat_of_row, int* __restrict__ row_token,
+                      float* __restrict__ row_weight) {
+  extern __shared__ int sh[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int run = blockIdx.x * kWarpsPerCta + warp;
+  if (run >= n_runs) return;
+  int* next = sh + warp * E;
+  for (int e = lane; e < E; e += 32) next[e] = start[static_cast<long long>(run) * E + e];
+  __syncwarp();
+  const long long base = static_cast<long long>(run) * kRun;
+  for (int i = 0; i < kRun; i += 32) {
+    const long long f = base + i + lane;
+    const bool valid = f < R;
+    int e = valid ? load_expert(idx, is_i64, f) : -1;
+    if (valid) e = e < 0 ? 0 : (e >= E ? E - 1 : e);
+    const unsigned peers = __match_any_sync(0xFFFFFFFFu, e);
+    const int rank = __popc(peers & ((1u << lane) - 1u));
+    int r = 0;
+    if (valid) r = next[e] + rank;
+    __syncwarp();
+    if (valid && rank == 0) next[e] += __popc(peers);
+    __syncwarp();
+    if (valid) {
+      const int p = pad_off[e] + (r - cum_excl[e]);
+      order[r] = static_cast<int>(f);
+      pad_pos[r] = p;
+      row_of_flat[f] = p;
+      flat_of_row[p] = static_cast<int>(f);
+      row_token[p] = static_cast<int>(f / k);
+      if (row_weight) row_weight[p] = weights_flat[f];
+    }
+  }
+}
+
+// One warp per token; 16-byte loads of bf16 rows, fp32 accumulation in slot order.
+__global__ void __launch_bounds__(256)
+combine_topk_kernel(const __nv_bfloat16* __restrict__ y_rows, const int* __restrict__ row_of_flat,
+                    const __nv_bfloat16* __restrict__ shared_out, __nv_bfloat16* __restrict__ out,
+                    long long T, int k, int D) {
+  const int lane = threadIdx.x & 31;
+  const long long warp0 = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const long long nwarps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
+  const int nchunks = D >> 3;
+  for (long long t = warp0; t < T; t += nwarps) {
+    for (int c = lane; c < nchunks; c += 32) {
+      float acc[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+      for (int j = 0; j < k; ++j) {
+        const int row = row_of_flat[t * k + j];
+        if (row < 0) continue;
+        const uint4 v = __ldg(reinterpret_cast<const uint4*>(
+            y_rows + static_cast<long long>(row) * D + c * 8));
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          acc[2 * i] += __uint_as_float(w[i] << 16);
+          acc[2 * i + 1] += __uint_as_float(w[i] & 0xFFFF0000u);
+        }
+      }
+      if (shared_out) {
+        const uint4 v = __ldg(reinterpret_cast<const uint4*>(shared_out + t * D + c * 8));
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          acc[2 * i] += __uint_as_float(w[i] << 16);
+          acc[2 * i + 1] += __uint_as_float(w[i] & 0xFFFF0000u);
+        }
+      }
+      uint32_t o[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const __nv_bfloat162 b = __floats2bfloat162_rn(acc[2 * i], acc[2 * i + 1]);
+        o[i] = *reinterpret_cast<const uint32_t*>(&b);
+      }
+      *reinterpret_cast<uint4*>(out + t * D + c * 8) = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+  }
+}
+
+}  // namespace nv41
+
+using namespace nv41;
+
+extern "C" long long nv41_moe_layout_workspace_bytes(long long R, int E) {
+  if (R < 0 || E <= 0) return NV41_ERR_INVALID;
+  const long long n_runs = (R + kRun - 1) / kRun;
+  return (n_runs > 0 ? n_runs : 1) * E * static_cast<long long>(sizeof(int));
+}
+
+extern "C" int nv41_moe_layout_build(const void* expert_idx, int idx_is_i64,
+                                     const float* weights_flat, long long R, int E, int k,
+                                     long long P_max, void* workspace, int* counts, int* cum_excl,
+                                     int* pad_off, int* order, int* pad_pos, int* row_of_flat,
+                                     int* flat_of_row, int* row_token, float* row_weight,
+                                     int* tile_expert, int* meta, int* status, void* stream) {
+  if (!expert_idx || R < 0 || E <= 0 || E > 2048 || k <= 0 || !workspace || !counts ||
+      !cum_excl || !pad_off || !order || !pad_pos || !row_of_flat || !flat_of_row ||
+      !row_token || !tile_expert || !meta || !status)
+    return NV41_ERR_INVALID;
+  if (P_max % 128 != 0 || P_max < R + 0) return NV41_ERR_INVALID;
+  if (row_weight && !weights_flat) return NV41_ERR_INVALID;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int n_runs = static_cast<int>((R + kRun - 1) / kRun);
+  const int n_tiles_max = static_cast<int>(P_max / 128);
+  const int ctas = n_runs > 0 ? (n_runs + kWarpsPerCta - 1) / kWarpsPerCta : 1;
+  const size_t sh_warp = static_cast<size_t>(kWarpsPerCta) * E * sizeof(int);
+  if (sh_warp > 48 * 1024) return NV41_ERR_UNSUPPORTED;
+  int* hist = static_cast<int*>(workspace);
+  layout_hist_kernel<<<ctas, kWarpsPerCta * 32, sh_warp, st>>>(
+      expert_idx, idx_is_i64, R, E, n_runs, hist, P_max, flat_of_row, row_token, row_weight,
+      status);
+  layout_scan_kernel<<<1, 1024, (3 * E + 2) * sizeof(int), st>>>(
+      hist, n_runs, E, R, n_tiles_max, counts, cum_excl, pad_off, tile_expert, meta);
+  if (n_runs > 0) {
+    layout_scatter_kernel<<<ctas, kWarpsPerCta * 32, sh_warp, st>>>(
+        expert_idx, idx_is_i64, weights_flat, R, E, k, n_runs, hist, cum_excl, pad_off, order,
+        pad_pos, row_of_flat, flat_of_row, row_token, row_weight);
+  }
+  return launch_status();
+}
+
+extern "C" int nv41_moe_combine(const void* y_rows_bf16, const int* row_of_flat,
+                                const void* shared_bf16, void* out_bf16, long long T, int k,
+                                int D, void* stream) {
+  if (!y_rows_bf16 || !row_of_flat || !out_bf16 || T < 0 || k <= 0 || D <= 0 || (D % 8) != 0)
+    return NV41_ERR_INVALID;
+  if (T == 0) return NV41_OK;
+  long long blocks = (T + 7) / 8;
+  const long long cap = 148LL * 16;
+  if (blocks > cap) blocks = cap;
+  combine_topk_kernel<<<static_cast<unsigned>(blocks), 256, 0,
+                        static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(y_rows_bf16), row_of_flat,
+      static_cast<const __nv_bfloat16*>(shared_bf16), static_cast<__nv_bfloat16*>(out_bf16), T,
+      k, D);
+  return launch_status();
+}

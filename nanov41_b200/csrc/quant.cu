@@ -1,0 +1,297 @@
+// Block quantizers of the MoE expert path (HBM-bound; all arithmetic in registers, block
+// maxima by warp shuffles).
+//
+//  * FP8-e4m3 1x128 activation quantizer: same arithmetic as the reference TileLang kernel
+//    ref/kernel.py:40-95 (act_quant, scale_fmt=None):  amax = max(|x|) over the 128 block,
+//    amax = max(amax, 1e-4), s = amax * fl32(1/448)  (a multiply, not a division),
+//    code = e4m3_rn_satfinite(clamp(x / s, -448, 448)) with an IEEE fp32 division.
+//  * FP8-e4m3 128x128 weight quantizer: the same arithmetic over 128x128 blocks; the scale
+//    tensor has the layout ref/kernel.py:232,259-264 consumes ([ceil(N/128), ceil(K/128)] fp32).
+//  * NVFP4-e2m1 1x16 quantizer: experiments/tl_kernels/nvfp4_gemm.py:78-126 (quantize_nvfp4),
+//    ties toward zero, e4m3 block scale, optional fp32 per-tensor global scale divided out first.
+//
+// No fast-math in this translation unit: codes and scales are compared bit-for-bit.
+#include <cuda_bf16.h>
+#include <cuda_fp8.h>
+#include <cstdint>
+
+#include "../../include/nanov41_b200.h"
+#include "util.cuh"
+
+namespace nv41 {
+
+__device__ __forceinline__ void unpack_bf16x8(const uint4& v, float (&f)[8]) {
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    f[2 * i] = __uint_as_float(w[i] << 16);
+    f[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+  }
+}
+
+// e4m3 code of clamp(x / s, +-448), round-to-nearest-even, saturating.
+__device__ __forceinline__ uint32_t fp8x4_codes(float a, float b, float c, float d, float s) {
+  float q0 = fminf(fmaxf(__fdiv_rn(a, s), -448.f), 448.f);
+  float q1 = fminf(fmaxf(__fdiv_rn(b, s), -448.f), 448.f);
+  float q2 = fminf(fmaxf(__fdiv_rn(c, s), -448.f), 448.f);
+  float q3 = fminf(fmaxf(__fdiv_rn(d, s), -448.f), 448.f);
+  uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(q0, q1), __NV_SATFINITE, __NV_E4M3);
+  uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(q2, q3), __NV_SATFINITE, __NV_E4M3);
+  return lo | (hi << 16);
+}
+
+// ------------------------------------------------------------------------- FP8 1x128 rows
+// One half-warp (16 lanes x 8 elements) per 1x128 block.  Work item = (row, k-block),
+// k-block fastest.  `gather` (optional) maps output row -> source row (-1 = all-zero row).
+__global__ void __launch_bounds__(256)
+quant_fp8_1x128_kernel(const __nv_bfloat16* __restrict__ x, long long ld_x,
+                       const int* __restrict__ gather, uint8_t* __restrict__ codes,
+                       float* __restrict__ scales, long long ss_row, long long ss_kb,
+                       long long rows, int K, int Kpad) {
+  const int nkb = Kpad / 128;
+  const long long n_items = rows * nkb;
+  const int lane = threadIdx.x & 31;
+  const int sub = lane & 15;            // position inside the block: elements [sub*8, sub*8+8)
+  const long long half_id =
+      (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 4;
+  const long long n_halves = (static_cast<long long>(gridDim.x) * blockDim.x) >> 4;
+  const float inv448 = 1.0f / 448.0f;   // fl32(1/448), folded at compile time
+
+  const unsigned hmask = 0xFFFFu << (lane & 16);   // shuffles stay inside the half-warp
+  for (long long item = half_id; item < n_items; item += n_halves) {
+    const long long row = item / nkb;
+    const int kb = static_cast<int>(item - row * nkb);
+    float f[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) f[i] = 0.f;
+    {
+      const int col = kb * 128 + sub * 8;
+      const long long src = gather ? static_cast<long long>(gather[row]) : row;
+      if (src >= 0 && col < K) {  // K % 8 == 0, so a chunk is entirely inside or outside
+        const uint4 v = __ldg(reinterpret_cast<const uint4*>(x + src * ld_x + col));
+        unpack_bf16x8(v, f);
+      }
+    }
+    float amax = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(f[i]));
+#pragma unroll
+    for (int o = 8; o >= 1; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(hmask, amax, o));
+    amax = fmaxf(amax, 1e-4f);
+    const float s = amax * inv448;
+    uint2 out;
+    out.x = fp8x4_codes(f[0], f[1], f[2], f[3], s);
+    out.y = fp8x4_codes(f[4], f[5], f[6], f[7], s);
+    *reinterpret_cast<uint2*>(codes + row * Kpad + kb * 128 + sub * 8) = out;
+    if (sub == 0) scales[row * ss_row + kb * ss_kb] = s;
+  }
+}
+
+// ------------------------------------------------------------------------- FP8 128x128 blocks
+// One CTA (256 threads) per 128x128 block of one expert's [N, K] matrix.  Writes the codes in
+// the source orientation ([E*N, Kpad], K contiguous) and, when codes_t != nullptr, also the
+// transposed copy ([E*Kpad, Npad], N contiguous, Npad = N rounded up to 128, zero filled) that the backward GEMMs read as their
+// K-major B operand.  The block scale is invariant under transposition.
+__global__ void __launch_bounds__(256)
+quant_fp8_128x128_kernel(const __nv_bfloat16* __restrict__ w, int E, int N, int K, int Kpad,
+                         int Npad, uint8_t* __restrict__ codes, uint8_t* __restrict__ codes_t,
+                         float* __restrict__ scales) {
+  __shared__ float red[8];
+  __shared__ float s_scale;
+  __shared__ __align__(16) uint8_t tile[128][128 + 16];
+  const int kb = blockIdx.x, nb = blockIdx.y, e = blockIdx.z;
+  const int nkb = Kpad / 128, nnb = (N + 127) / 128;
+  const int tid = threadIdx.x;
+  const int chunk = tid & 15;          // 16 chunks of 8 elements across the 128 columns
+  const int r0 = tid >> 4;             // 16 rows per pass, 8 passes
+  const int col = kb * 128 + chunk * 8;
+  float f[8][8];
+  float amax = 0.f;
+#pragma unroll
+  for (int p = 0; p < 8; ++p) {
+    const int r = nb * 128 + p * 16 + r0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) f[p][i] = 0.f;
+    if (r < N && col < K) {
+      const uint4 v = __ldg(reinterpret_cast<const uint4*>(
+          w + (static_cast<long long>(e) * N + r) * K + col));
+      unpack_bf16x8(v, f[p]);
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(f[p][i]));
+  }
+#pragma unroll
+  for (int o = 16; o >= 1; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
+  if ((tid & 31) == 0) red[tid >> 5] = amax;
+  __syncthreads();
+  if (tid == 0) {
+    float m = red[0];
+#pragma unroll
+    for (int i = 1; i < 8; ++i) m = fmaxf(m, red[i]);
+    m = fmaxf(m, 1e-4f);
+    const float s = m * (1.0f / 448.0f);
+    s_scale = s;
+    scales[(static_cast<long long>(e) * nnb + nb) * nkb + kb] = s;
+  }
+  __syncthreads();
+  const float s = s_scale;
+#pragma unroll
+  for (int p = 0; p < 8; ++p) {
+    const int rl = p * 16 + r0;
+    const int r = nb * 128 + rl;
+    uint2 out;
+    out.x = fp8x4_codes(f[p][0], f[p][1], f[p][2], f[p][3], s);
+    out.y = fp8x4_codes(f[p][4], f[p][5], f[p][6], f[p][7], s);
+    if (r < N) {
+      *reinterpret_cast<uint2*>(codes + (static_cast<long long>(e) * N + r) * Kpad + col) = out;
+    }
+    if (codes_t) *reinterpret_cast<uint2*>(&tile[rl][chunk * 8]) = out;
+  }
+  if (codes_t) {
+    __syncthreads();
+    // transposed store: thread -> (k-row = tid/2 within the block, 64 n-values = half a row)
+    const int kr = tid >> 1, nh = (tid & 1) * 64;
+    const long long krow = static_cast<long long>(e) * Kpad + kb * 128 + kr;
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      uint32_t wds[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        uint32_t wd = 0;
+#pragma unroll
+        for (int b = 0; b < 4; ++b)
+          wd |= static_cast<uint32_t>(tile[nh + c * 16 + j * 4 + b][kr]) << (8 * b);
+        wds[j] = wd;
+      }
+      const int n = nb * 128 + nh + c * 16;
+      if (n < Npad) {
+        *reinterpret_cast<uint4*>(codes_t + krow * Npad + n) =
+            make_uint4(wds[0], wds[1], wds[2], wds[3]);
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------------- NVFP4 1x16 blocks
+// One lane per 16-element block.  code = (#boundaries strictly below min(|q|, 6)) with
+// boundaries {0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5}  (ties go toward zero), +8 when the value is
+// negative and the magnitude index is non-zero.  Packed low nibble = even column.
+__device__ __forceinline__ uint32_t e2m1_code(float q) {
+  const float a = fminf(fabsf(q), 6.0f);
+  uint32_t idx = (a > 0.25f) + (a > 0.75f) + (a > 1.25f) + (a > 1.75f) + (a > 2.5f) +
+                 (a > 3.5f) + (a > 5.0f);
+  return idx | ((q < 0.f && idx != 0u) ? 8u : 0u);
+}
+
+template <bool kInputFp32>
+__global__ void __launch_bounds__(256)
+quant_nvfp4_1x16_kernel(const void* __restrict__ xin, long long rows, int K, float global_scale,
+                        uint8_t* __restrict__ packed, uint8_t* __restrict__ scale_bytes) {
+  const int nblk = K / 16;
+  const long long n_items = rows * nblk;
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long item = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+       item < n_items; item += stride) {
+    float f[16];
+    if (kInputFp32) {
+      const float4* p = reinterpret_cast<const float4*>(
+          reinterpret_cast<const float*>(xin) + item * 16);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float4 v = __ldg(p + i);
+        f[4 * i] = v.x; f[4 * i + 1] = v.y; f[4 * i + 2] = v.z; f[4 * i + 3] = v.w;
+      }
+    } else {
+      const uint4* p = reinterpret_cast<const uint4*>(
+          reinterpret_cast<const __nv_bfloat16*>(xin) + item * 16);
+      float lo[8], hi[8];
+      unpack_bf16x8(__ldg(p), lo);
+      unpack_bf16x8(__ldg(p + 1), hi);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) { f[i] = lo[i]; f[8 + i] = hi[i]; }
+    }
+    if (global_scale != 1.0f) {
+#pragma unroll
+      for (int i = 0; i < 16; ++i) f[i] = __fdiv_rn(f[i], global_scale);
+    }
+    float amax = 0.f;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(f[i]));
+    amax = fmaxf(amax, 1e-8f);
+    // e4m3 block scale: round-to-nearest-even of amax / 6 (saturating at 448)
+    const __nv_fp8_storage_t sb =
+        __nv_cvt_float_to_fp8(__fdiv_rn(amax, 6.0f), __NV_SATFINITE, __NV_E4M3);
+    const __half_raw hr = __nv_cvt_fp8_to_halfraw(sb, __NV_E4M3);
+    float s = __half2float(__half(hr));
+    s = fmaxf(s, 0.001953125f);  // 2^-9, the smallest e4m3 subnormal
+    uint32_t words[2] = {0u, 0u};
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const uint32_t c = e2m1_code(__fdiv_rn(f[i], s));
+      words[i >> 3] |= c << (4 * (i & 7));
+    }
+    *reinterpret_cast<uint2*>(packed + item * 8) = make_uint2(words[0], words[1]);
+    // the stored byte is the e4m3 encoding of the clamped scale (2^-9 encodes as 0x01)
+    scale_bytes[item] = (s == 0.001953125f) ? static_cast<uint8_t>(0x01) : static_cast<uint8_t>(sb);
+  }
+}
+
+}  // namespace nv41
+
+using namespace nv41;
+
+extern "C" int nv41_quant_fp8_1x128(const void* x_bf16, long long ld_x, const int* gather_rows,
+                                    long long rows, int K, void* codes, float* scales,
+                                    long long scale_stride_row, long long scale_stride_kb,
+                                    void* stream) {
+  if (!x_bf16 || !codes || !scales || rows < 0 || K <= 0 || (K % 8) != 0 || ld_x < K)
+    return NV41_ERR_INVALID;
+  if (rows == 0) return NV41_OK;
+  const int Kpad = (K + 127) / 128 * 128;
+  const long long items = rows * (Kpad / 128);
+  long long blocks = (items * 16 + 255) / 256;
+  const long long cap = 148LL * 8 * 4;
+  if (blocks > cap) blocks = cap;
+  quant_fp8_1x128_kernel<<<static_cast<unsigned>(blocks), 256, 0,
+                           static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(x_bf16), ld_x, gather_rows,
+      static_cast<uint8_t*>(codes), scales, scale_stride_row, scale_stride_kb, rows, K, Kpad);
+  return launch_status();
+}
+
+extern "C" int nv41_quant_fp8_128x128(const void* w_bf16, int E, int N, int K, void* codes,
+                                      void* codes_t, float* scales, void* stream) {
+  if (!w_bf16 || !codes || !scales || E <= 0 || N <= 0 || K <= 0 || (K % 8) != 0)
+    return NV41_ERR_INVALID;
+  const int Kpad = (K + 127) / 128 * 128;
+  const int Npad = (N + 127) / 128 * 128;   // the transposed copy is a K operand: pad to blocks
+  dim3 grid(Kpad / 128, (N + 127) / 128, E);
+  quant_fp8_128x128_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(w_bf16), E, N, K, Kpad, Npad,
+      static_cast<uint8_t*>(codes), static_cast<uint8_t*>(codes_t), scales);
+  return launch_status();
+}
+
+extern "C" int nv41_quant_nvfp4_1x16(const void* x, int x_is_fp32, long long rows, int K,
+                                     float global_scale, void* packed, void* scale_bytes,
+                                     void* stream) {
+  if (!x || !packed || !scale_bytes || rows < 0 || K <= 0 || (K % 16) != 0 ||
+      !(global_scale > 0.f))
+    return NV41_ERR_INVALID;
+  if (rows == 0) return NV41_OK;
+  const long long items = rows * (K / 16);
+  long long blocks = (items + 255) / 256;
+  const long long cap = 148LL * 8 * 8;
+  if (blocks > cap) blocks = cap;
+  if (x_is_fp32)
+    quant_nvfp4_1x16_kernel<true><<<static_cast<unsigned>(blocks), 256, 0,
+                                    static_cast<cudaStream_t>(stream)>>>(
+        x, rows, K, global_scale, static_cast<uint8_t*>(packed),
+        static_cast<uint8_t*>(scale_bytes));
+  else
+    quant_nvfp4_1x16_kernel<false><<<static_cast<unsigned>(blocks), 256, 0,
+                                     static_cast<cudaStream_t>(stream)>>>(
+        x, rows, K, global_scale, static_cast<uint8_t*>(packed),
+        static_cast<uint8_t*>(scale_bytes));
+  return launch_status();
+}

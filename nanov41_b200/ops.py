@@ -1,0 +1,303 @@
+"""Torch-facing wrappers over the C ABI: they allocate outputs with the caching allocator, pass
+raw device pointers and the current CUDA stream to libnanov41_b200.so, and never synchronise.
+
+No operator here has a CPU or eager-PyTorch fallback: a tensor that is not on a CUDA device, or
+a missing shared library, raises.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+
+import torch
+
+from . import _lib
+from ._lib import Nv41Error, check
+
+A_CONTIGUOUS, A_GATHER_FP8 = 0, 1
+BM = 128
+
+
+def _ptr(t):
+    return None if t is None else C.c_void_p(t.data_ptr())
+
+
+def _stream():
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _need_cuda(*tensors):
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise Nv41Error("nanov41_b200 operators run on CUDA tensors only (no CPU fallback)")
+
+
+def ceil_to(v: int, m: int) -> int:
+    return (v + m - 1) // m * m
+
+
+# --------------------------------------------------------------------------------- status word
+_STATUS: dict[int, torch.Tensor] = {}
+
+
+def status_word(device) -> torch.Tensor:
+    """Per-device 32-bit word the GEMM kernels write when a bounded wait runs out."""
+    idx = torch.device(device).index
+    if idx is None:
+        idx = torch.cuda.current_device()
+    if idx not in _STATUS:
+        _STATUS[idx] = torch.zeros(1, dtype=torch.int32, device=f"cuda:{idx}")
+    return _STATUS[idx]
+
+
+def check_status(device=None) -> None:
+    """Synchronise and raise if any kernel on `device` reported a timed-out wait."""
+    st = status_word(device if device is not None else torch.cuda.current_device())
+    raw = C.c_uint(0)
+    with torch.cuda.device(st.device):
+        rc = _lib.load().nv41_status_read(_ptr(st), C.byref(raw), _stream())
+    if rc != _lib.OK:
+        st.zero_()
+        raise Nv41Error(f"device status word = 0x{raw.value:08x} "
+                        f"(code {raw.value >> 24}, cta {raw.value & 0xFFFFFF}), rc={rc}")
+
+
+# --------------------------------------------------------------------------------- quantizers
+def quant_fp8_1x128(x: torch.Tensor, gather: torch.Tensor | None = None, rows: int | None = None,
+                    scale_kmajor: bool = False):
+    """bf16 [n, K] -> (e4m3 codes as uint8 [rows, Kpad], fp32 scales).
+
+    Scales are [rows, Kpad/128] (the reference's layout) or, with ``scale_kmajor``,
+    [Kpad/128, rows] (what the grouped GEMMs read).  ``gather`` (int32 [rows]) selects source
+    rows; -1 gives an all-zero row."""
+    _need_cuda(x, gather)
+    if x.dtype != torch.bfloat16 or x.dim() != 2 or x.stride(1) != 1:
+        raise Nv41Error("quant_fp8_1x128 expects a 2-D bf16 tensor with unit inner stride")
+    K = x.shape[1]
+    n_rows = (gather.numel() if gather is not None else x.shape[0]) if rows is None else rows
+    kpad = ceil_to(K, 128)
+    codes = torch.empty((n_rows, kpad), dtype=torch.uint8, device=x.device)
+    if scale_kmajor:
+        scales = torch.empty((kpad // 128, n_rows), dtype=torch.float32, device=x.device)
+        ss_row, ss_kb = 1, n_rows
+    else:
+        scales = torch.empty((n_rows, kpad // 128), dtype=torch.float32, device=x.device)
+        ss_row, ss_kb = kpad // 128, 1
+    check(_lib.load().nv41_quant_fp8_1x128(_ptr(x), x.stride(0), _ptr(gather), n_rows, K,
+                                           _ptr(codes), _ptr(scales), ss_row, ss_kb, _stream()),
+          "nv41_quant_fp8_1x128")
+    return codes, scales
+
+
+def quant_fp8_128x128(w: torch.Tensor, transposed: bool = False):
+    """bf16 [E, N, K] -> (codes uint8 [E, N, Kpad], scales fp32 [E, ceil(N/128), Kpad/128]
+    [, codes_t uint8 [E, Kpad, Npad]])."""
+    _need_cuda(w)
+    if w.dtype != torch.bfloat16 or w.dim() != 3 or not w.is_contiguous():
+        raise Nv41Error("quant_fp8_128x128 expects a contiguous 3-D bf16 tensor")
+    E, N, K = w.shape
+    kpad, npad = ceil_to(K, 128), ceil_to(N, 128)
+    codes = torch.empty((E, N, kpad), dtype=torch.uint8, device=w.device)
+    scales = torch.empty((E, npad // 128, kpad // 128), dtype=torch.float32, device=w.device)
+    codes_t = torch.empty((E, kpad, npad), dtype=torch.uint8, device=w.device) if transposed else None
+    check(_lib.load().nv41_quant_fp8_128x128(_ptr(w), E, N, K, _ptr(codes), _ptr(codes_t),
+                                             _ptr(scales), _stream()), "nv41_quant_fp8_128x128")
+    return (codes, scales, codes_t) if transposed else (codes, scales)
+
+
+def quant_nvfp4_1x16(x: torch.Tensor, global_scale: float = 1.0):
+    """bf16/fp32 [rows, K] -> (packed e2m1 uint8 [rows, K/2], e4m3 scale bytes uint8 [rows, K/16])."""
+    _need_cuda(x)
+    if x.dtype not in (torch.bfloat16, torch.float32) or x.dim() != 2 or not x.is_contiguous():
+        raise Nv41Error("quant_nvfp4_1x16 expects a contiguous 2-D bf16 or fp32 tensor")
+    rows, K = x.shape
+    if K % 16:
+        raise Nv41Error("quant_nvfp4_1x16: K must be a multiple of 16")
+    packed = torch.empty((rows, K // 2), dtype=torch.uint8, device=x.device)
+    sbytes = torch.empty((rows, K // 16), dtype=torch.uint8, device=x.device)
+    check(_lib.load().nv41_quant_nvfp4_1x16(_ptr(x), int(x.dtype == torch.float32), rows, K,
+                                            float(global_scale), _ptr(packed), _ptr(sbytes),
+                                            _stream()), "nv41_quant_nvfp4_1x16")
+    return packed, sbytes
+
+
+# --------------------------------------------------------------------------------- layout
+@dataclass
+class DeviceLayout:
+    """Device-resident router-sorted layout (all int32 unless noted)."""
+    T: int
+    k: int
+    E: int
+    R: int
+    P_max: int
+    counts: torch.Tensor
+    cum_excl: torch.Tensor
+    pad_off: torch.Tensor
+    order: torch.Tensor
+    pad_pos: torch.Tensor
+    row_of_flat: torch.Tensor
+    flat_of_row: torch.Tensor
+    row_token: torch.Tensor
+    row_weight: torch.Tensor | None
+    tile_expert: torch.Tensor
+    meta: torch.Tensor
+    status: torch.Tensor
+
+
+def p_max_for(R: int, E: int) -> int:
+    """Rows allocated for the padded space (nanov41/triton_grouped_moe.py:473-474, BM = 128)."""
+    return ((R + E * BM) // BM) * BM
+
+
+def build_layout(flat_expert: torch.Tensor, n_experts: int, k: int,
+                 weights_flat: torch.Tensor | None = None) -> DeviceLayout:
+    _need_cuda(flat_expert, weights_flat)
+    if flat_expert.dtype not in (torch.int64, torch.int32):
+        raise Nv41Error("expert indices must be int64 or int32")
+    idx = flat_expert.reshape(-1).contiguous()
+    R = idx.numel()
+    if R % k:
+        raise Nv41Error("number of routed rows is not a multiple of k")
+    dev = idx.device
+    P = p_max_for(R, n_experts)
+    lib = _lib.load()
+    ws_bytes = lib.nv41_moe_layout_workspace_bytes(R, n_experts)
+    if ws_bytes < 0:
+        raise Nv41Error("nv41_moe_layout_workspace_bytes: invalid arguments")
+    i32 = dict(dtype=torch.int32, device=dev)
+    workspace = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
+    counts = torch.empty(n_experts, **i32)
+    cum_excl = torch.empty(n_experts + 1, **i32)
+    pad_off = torch.empty(n_experts + 1, **i32)
+    order = torch.empty(R, **i32)
+    pad_pos = torch.empty(R, **i32)
+    row_of_flat = torch.empty(R, **i32)
+    flat_of_row = torch.empty(P, **i32)
+    row_token = torch.empty(P, **i32)
+    row_weight = None
+    if weights_flat is not None:
+        weights_flat = weights_flat.reshape(-1).float().contiguous()
+        row_weight = torch.empty(P, dtype=torch.float32, device=dev)
+    tile_expert = torch.empty(P // BM, **i32)
+    meta = torch.empty(4, **i32)
+    status = torch.zeros(1, **i32)
+    check(lib.nv41_moe_layout_build(_ptr(idx), int(idx.dtype == torch.int64), _ptr(weights_flat),
+                                    R, n_experts, k, P, _ptr(workspace), _ptr(counts),
+                                    _ptr(cum_excl), _ptr(pad_off), _ptr(order), _ptr(pad_pos),
+                                    _ptr(row_of_flat), _ptr(flat_of_row), _ptr(row_token),
+                                    _ptr(row_weight), _ptr(tile_expert), _ptr(meta), _ptr(status),
+                                    _stream()), "nv41_moe_layout_build")
+    return DeviceLayout(R // k, k, n_experts, R, P, counts, cum_excl, pad_off, order, pad_pos,
+                        row_of_flat, flat_of_row, row_token, row_weight, tile_expert, meta, status)
+
+
+def combine(y_rows: torch.Tensor, row_of_flat: torch.Tensor, T: int, k: int,
+            shared: torch.Tensor | None = None) -> torch.Tensor:
+    """out[t] = bf16(sum_j fp32(y_rows[row_of_flat[t*k+j]]) + fp32(shared[t]))."""
+    _need_cuda(y_rows, row_of_flat, shared)
+    D = y_rows.shape[1]
+    if y_rows.dtype != torch.bfloat16 or not y_rows.is_contiguous():
+        raise Nv41Error("combine expects contiguous bf16 rows")
+    if shared is not None:
+        shared = shared.to(torch.bfloat16).contiguous()
+    out = torch.empty((T, D), dtype=torch.bfloat16, device=y_rows.device)
+    check(_lib.load().nv41_moe_combine(_ptr(y_rows), _ptr(row_of_flat), _ptr(shared), _ptr(out),
+                                       T, k, D, _stream()), "nv41_moe_combine")
+    return out
+
+
+# --------------------------------------------------------------------------------- GEMMs
+def gemm1_fp8(a_mode: int, a_codes: torch.Tensor, a_scale_kmajor: torch.Tensor,
+              w13_codes: torch.Tensor, w13_scale: torch.Tensor, layout: DeviceLayout,
+              limit: float, save_gate_up: bool = False, save_h: bool = False):
+    """Gate/up grouped GEMM + SwiGLU + 1x128 re-quantisation of h.
+
+    a_codes: uint8 [P_max, K] (A_CONTIGUOUS) or [T, K] (A_GATHER_FP8); a_scale_kmajor: fp32
+    [K/128, rows-or-tokens]; w13_codes: uint8 [E, 2I, K]; w13_scale: fp32 [E, 2I/128, K/128].
+    Returns (h_codes uint8 [P_max, I], h_scale fp32 [I/128, P_max], gate, up, h) with the
+    last three bf16 [P_max, I] or None."""
+    _need_cuda(a_codes, a_scale_kmajor, w13_codes, w13_scale)
+    E, twoI, K = w13_codes.shape
+    I = twoI // 2
+    P = layout.P_max
+    dev = a_codes.device
+    h_codes = torch.empty((P, I), dtype=torch.uint8, device=dev)
+    h_scale = torch.empty((I // 128, P), dtype=torch.float32, device=dev)
+    gate = torch.empty((P, I), dtype=torch.bfloat16, device=dev) if save_gate_up else None
+    up = torch.empty((P, I), dtype=torch.bfloat16, device=dev) if save_gate_up else None
+    h = torch.empty((P, I), dtype=torch.bfloat16, device=dev) if save_h else None
+    st = status_word(dev)
+    check(_lib.load().nv41_moe_gemm1_fp8(
+        a_mode, _ptr(a_codes), a_codes.stride(0), K, _ptr(a_scale_kmajor),
+        a_scale_kmajor.stride(0), a_codes.shape[0], _ptr(w13_codes), _ptr(w13_scale), E, I, K,
+        _ptr(layout.tile_expert), _ptr(layout.row_token), _ptr(layout.row_weight), P,
+        float(limit), _ptr(h_codes), _ptr(h_scale), _ptr(gate), _ptr(up), _ptr(h), _ptr(st),
+        _stream()), "nv41_moe_gemm1_fp8")
+    return h_codes, h_scale, gate, up, h
+
+
+def gemm_fp8(a_mode: int, a_codes: torch.Tensor, a_scale_kmajor: torch.Tensor,
+             b_codes: torch.Tensor, b_scale: torch.Tensor, layout: DeviceLayout,
+             b_scale_transposed: bool = False) -> torch.Tensor:
+    """Grouped C = A @ B_e^T (bf16 [P_max, N]); b_codes uint8 [E, N, K]; b_scale fp32
+    [E, ceil(N/128), K/128], or [E, K/128, ceil(N/128)] with ``b_scale_transposed``."""
+    _need_cuda(a_codes, a_scale_kmajor, b_codes, b_scale)
+    E, N, K = b_codes.shape
+    P = layout.P_max
+    out = torch.empty((P, N), dtype=torch.bfloat16, device=a_codes.device)
+    bs_e = b_scale.stride(0)
+    if b_scale_transposed:
+        bs_nb, bs_kb = b_scale.stride(2), b_scale.stride(1)
+    else:
+        bs_nb, bs_kb = b_scale.stride(1), b_scale.stride(2)
+    st = status_word(a_codes.device)
+    check(_lib.load().nv41_moe_gemm_fp8(
+        a_mode, _ptr(a_codes), a_codes.stride(0), _ptr(a_scale_kmajor),
+        a_scale_kmajor.stride(0), a_codes.shape[0], _ptr(b_codes), _ptr(b_scale), bs_e, bs_nb,
+        bs_kb, E, N, K, _ptr(layout.tile_expert), _ptr(layout.row_token), P, _ptr(out),
+        out.stride(0), _ptr(st), _stream()), "nv41_moe_gemm_fp8")
+    return out
+
+
+# --------------------------------------------------------------------------------- layer
+@dataclass
+class Fp8ExpertWeights:
+    """Block-quantised expert weights: W13 = [W1; W3] per expert, and W2."""
+    w13_codes: torch.Tensor   # uint8 [E, 2I, Dpad]
+    w13_scale: torch.Tensor   # fp32 [E, 2I/128, Dpad/128]
+    w2_codes: torch.Tensor    # uint8 [E, D, Ipad]
+    w2_scale: torch.Tensor    # fp32 [E, ceil(D/128), Ipad/128]
+    E: int
+    I: int
+    D: int
+
+
+def quantize_expert_weights(w1: torch.Tensor, w3: torch.Tensor, w2: torch.Tensor) -> Fp8ExpertWeights:
+    """w1, w3: bf16 [E, I, D]; w2: bf16 [E, D, I] (the [out, in] orientation Linear stores)."""
+    E, I, D = w1.shape
+    w13 = torch.cat((w1, w3), dim=1).contiguous()
+    c13, s13 = quant_fp8_128x128(w13)
+    c2, s2 = quant_fp8_128x128(w2.contiguous())
+    return Fp8ExpertWeights(c13, s13, c2, s2, E, I, D)
+
+
+def moe_forward_fp8(x: torch.Tensor, wq: Fp8ExpertWeights, weights: torch.Tensor,
+                    indices: torch.Tensor, limit: float, shared: torch.Tensor | None = None,
+                    layout: DeviceLayout | None = None, return_parts: bool = False):
+    """Routed-experts forward in FP8: quantise x once per token, gate/up GEMM with the rows
+    fetched by token + SwiGLU + re-quantised h, down GEMM, fp32 top-k combine (+ shared)."""
+    _need_cuda(x, weights, indices)
+    T, D = x.shape
+    k = indices.shape[1]
+    if layout is None:
+        layout = build_layout(indices.reshape(-1), wq.E, k, weights.reshape(-1))
+    x_codes, x_scale = quant_fp8_1x128(x.contiguous(), scale_kmajor=True)
+    h_codes, h_scale, gate, up, h = gemm1_fp8(A_GATHER_FP8, x_codes, x_scale, wq.w13_codes,
+                                              wq.w13_scale, layout, limit,
+                                              save_gate_up=return_parts, save_h=return_parts)
+    y_rows = gemm_fp8(A_CONTIGUOUS, h_codes, h_scale, wq.w2_codes, wq.w2_scale, layout)
+    out = combine(y_rows, layout.row_of_flat, T, k, shared)
+    if return_parts:
+        return out, dict(layout=layout, x_codes=x_codes, x_scale=x_scale, h_codes=h_codes,
+                         h_scale=h_scale, gate=gate, up=up, h=h, y_rows=y_rows)
+    return out

@@ -1,0 +1,124 @@
+"""Oracle for the grouped expert SwiGLU MoE (CPU, torch).  Test infrastructure only.
+
+Two references live here:
+  * ``moe_bf16``   -- the reference's bf16 maths (nanov41/_ref_patched_model.py:858-868,906-921;
+    nanov41/fast_moe.py:419-474), pinned against its outputs in tests/golden/.
+  * ``moe_fp8``    -- the mixed-precision path: block-quantise, DEQUANTISE, fp32 matmul, with
+    the reference's rounding points (Linear output -> bf16, h -> bf16, fp32 combine, one final
+    bf16 rounding).  This is the dequantise-then-fp32-matmul oracle GEMM outputs are held to
+    (bf16 outputs: max rel err <= 2e-2, mean rel err <= 2e-3).
+"""
+from __future__ import annotations
+
+import torch
+import torch.nn.functional as F
+
+from . import quant as Q
+from .layout import sort_tokens
+
+
+def swiglu(gate: torch.Tensor, up: torch.Tensor, limit: float, weights=None) -> torch.Tensor:
+    """nanov41/fast_moe.py:341-350 / _ref_patched_model.py:860-867: fp32; up clamped both
+    sides, gate from above only; h = weights * (silu(gate) * up)."""
+    if limit is not None and limit > 0:
+        up = torch.clamp(up, min=-limit, max=limit)
+        gate = torch.clamp(gate, max=limit)
+    h = F.silu(gate) * up
+    if weights is not None:
+        h = weights * h
+    return h
+
+
+def moe_bf16(x, w1, w3, w2, weights, indices, limit, shared=None):
+    """Routed experts in the reference's bf16 arithmetic (sorted per-expert loop,
+    nanov41/fast_moe.py:419-450) + fp32 combine (:311-338) + shared expert add (:467-474).
+    x [T,D] bf16; w1,w3 [E,I,D]; w2 [E,D,I]; weights [T,k] fp32; indices [T,k] int64;
+    shared: optional bf16 [T,D] output of the shared expert.  Returns bf16 [T,D]."""
+    T, k = indices.shape
+    E = w1.shape[0]
+    order, tok, counts = sort_tokens(indices, E)
+    xs = x.index_select(0, tok)
+    ws = weights.reshape(-1).index_select(0, order)
+    outs = torch.empty(T * k, x.shape[1], dtype=x.dtype)
+    pos = 0
+    for e in range(E):
+        c = int(counts[e])
+        if c:
+            xe = xs[pos:pos + c]
+            gate = F.linear(xe, w1[e]).float()
+            up = F.linear(xe, w3[e]).float()
+            h = swiglu(gate, up, limit, ws[pos:pos + c, None])
+            outs[pos:pos + c] = F.linear(h.to(x.dtype), w2[e])
+        pos += c
+    flat = torch.empty(T * k, x.shape[1], dtype=torch.float32)
+    flat.index_copy_(0, order, outs.float())
+    y = flat.view(T, k, -1).sum(1)
+    if shared is not None:
+        y = y + shared
+    return y.to(x.dtype)
+
+
+def quantize_weights_fp8(w1, w3, w2):
+    """W13 = cat(w1, w3) per expert along the output dim (nanov41/fast_moe.py:371,385), then
+    128x128 block quantisation of W13 [E,2I,D] and W2 [E,D,I]."""
+    w13 = torch.cat((w1, w3), dim=1)
+    c13, s13 = Q.fp8_quant_128x128(w13)
+    c2, s2 = Q.fp8_quant_128x128(w2)
+    return (c13, s13), (c2, s2)
+
+
+def moe_fp8(x, w1, w3, w2, weights, indices, limit, shared=None, return_parts=False):
+    """Dequantise-then-fp32-matmul oracle of the FP8 expert path (forward).
+
+    x -> act_quant 1x128 (per token row) -> dequant -> @ dequant(W13)^T in fp32 -> bf16
+    -> fp32 SwiGLU (+clamp, x routing weight) -> bf16 h -> act_quant 1x128 -> dequant
+    -> @ dequant(W2)^T fp32 -> bf16 -> fp32 sum over slots (+ shared) -> bf16.
+    Scale semantics: ref/kernel.py:207-274 (fp8_gemm: C += (A_q B_q^T)_kblock * sa * sb)."""
+    T, k = indices.shape
+    E, I, D = w1.shape
+    (c13, s13), (c2, s2) = quantize_weights_fp8(w1, w3, w2)
+    w13d = Q.fp8_dequant_128x128(c13, s13)[:, :, :D]          # [E, 2I, D]
+    w2d = Q.fp8_dequant_128x128(c2, s2)[:, :, :I]             # [E, D, I]
+    xc, xsc = Q.fp8_quant_1x128(x)
+    xd = Q.fp8_dequant_1x128(xc, xsc)[:, :D]                  # [T, D] fp32
+    order, tok, counts = sort_tokens(indices, E)
+    ws = weights.reshape(-1).index_select(0, order)
+    R = T * k
+    gate_all = torch.zeros(R, I, dtype=torch.bfloat16)
+    up_all = torch.zeros(R, I, dtype=torch.bfloat16)
+    h_all = torch.zeros(R, I, dtype=torch.bfloat16)
+    outs = torch.zeros(R, D, dtype=torch.bfloat16)
+    pos = 0
+    for e in range(E):
+        c = int(counts[e])
+        if c:
+            xe = xd.index_select(0, tok[pos:pos + c])
+            gu = (xe @ w13d[e].t()).to(torch.bfloat16)
+            gate, up = gu[:, :I], gu[:, I:]
+            h = swiglu(gate.float(), up.float(), limit, ws[pos:pos + c, None]).to(torch.bfloat16)
+            hc, hs = Q.fp8_quant_1x128(h)
+            hd = Q.fp8_dequant_1x128(hc, hs)[:, :I]
+            outs[pos:pos + c] = (hd @ w2d[e].t()).to(torch.bfloat16)
+            gate_all[pos:pos + c], up_all[pos:pos + c], h_all[pos:pos + c] = gate, up, h
+        pos += c
+    flat = torch.empty(R, D, dtype=torch.float32)
+    flat.index_copy_(0, order, outs.float())
+    y = flat.view(T, k, D).sum(1)
+    if shared is not None:
+        y = y + shared
+    y = y.to(torch.bfloat16)
+    if return_parts:
+        return y, dict(order=order, tok=tok, counts=counts, gate=gate_all, up=up_all, h=h_all,
+                       outs=outs, x_codes=xc, x_scales=xsc, w13=(c13, s13), w2=(c2, s2))
+    return y
+
+
+def rel_errors(a: torch.Tensor, ref: torch.Tensor):
+    """(max rel, mean rel) = (max|a-ref|, mean|a-ref|) / max|ref| -- the normalisation of
+    tests/kernel_parity_fast_moe.py:68-75 (rel_err) extended with the mean."""
+    a, ref = a.float(), ref.float()
+    scale = ref.abs().max().item()
+    d = (a - ref).abs()
+    if scale == 0:
+        return d.max().item(), d.mean().item()
+    return d.max().item() / scale, d.mean().item() / scale

@@ -1,0 +1,135 @@
+"""CPU: pins the oracle against fixtures produced by the reference's own code
+(tests/golden/make_golden.py)."""
+import numpy as np
+import pytest
+import torch
+
+from conftest import bf16_from_bits
+from oracle import layout as OL
+from oracle import moe as OM
+from oracle import quant as OQ
+
+NVFP4_CASES = ["c0", "c1", "c2", "c3", "c4", "c5", "ties", "zeros"]
+
+
+@pytest.mark.parametrize("name", NVFP4_CASES)
+def test_nvfp4_oracle_bit_exact_vs_reference(golden, name):
+    g = golden("nvfp4_cases.npz")
+    x = bf16_from_bits(g[f"{name}_x"])
+    packed, sbytes = OQ.nvfp4_quant(x)
+    assert np.array_equal(packed.numpy(), g[f"{name}_packed"])
+    assert np.array_equal(sbytes.numpy(), g[f"{name}_scale"])
+    deq = OQ.nvfp4_dequant(packed, sbytes)
+    assert np.array_equal(deq.numpy(), g[f"{name}_deq"])
+
+
+def test_nvfp4_tie_rule_is_toward_zero(golden):
+    g = golden("nvfp4_cases.npz")
+    codes = g["ties_packed"][0, :8]
+    lo, hi = codes & 0xF, codes >> 4
+    seq = np.stack([lo, hi], 1).reshape(-1)
+    # 6, .25, .75, 1.25, 1.75, 2.5, 3.5, 5, then the negatives, then -0.0
+    assert seq.tolist() == [7, 0, 1, 2, 3, 4, 5, 6, 0, 9, 10, 11, 12, 13, 14, 0]
+
+
+def test_nvfp4_global_scale_one_is_identity():
+    x = (torch.randn(16, 64, generator=torch.Generator().manual_seed(1)) * 3).bfloat16()
+    a = OQ.nvfp4_quant(x, 1.0)
+    b = OQ.nvfp4_quant(x.float() * 0.5, 0.5)       # power-of-two scale: exact
+    assert torch.equal(a[0], b[0]) and torch.equal(a[1], b[1])
+
+
+@pytest.mark.parametrize("case", ["r0", "r1", "r2"])
+def test_fp8_divide_clamp_cast_matches_reference_row_quantizer(golden, case):
+    """nanov41/fp8_head.py:40-45 shares the divide/clamp/cast step with act_quant; given its
+    scale the codes must agree bit for bit."""
+    g = golden("fp8_cast_cases.npz")
+    x = bf16_from_bits(g[f"{case}_x"])
+    scale = torch.from_numpy(g[f"{case}_scale"])
+    codes = (x.float() / scale).clamp(-448, 448).to(torch.float8_e4m3fn).view(torch.uint8)
+    assert np.array_equal(codes.numpy(), g[f"{case}_codes"])
+    # and the oracle's own scale rule differs only by the multiply-vs-divide rounding
+    oc, osc = OQ.fp8_quant_1x128(x)
+    assert torch.allclose(osc[:, 0], scale[:, 0].clamp_min(1e-4 / 448), rtol=2e-7, atol=0)
+    assert (oc.numpy() != g[f"{case}_codes"]).mean() < 0.01
+
+
+def test_fp8_1x128_properties():
+    gen = torch.Generator().manual_seed(0)
+    x = torch.randn(37, 384, generator=gen).bfloat16()
+    x[3] = 0
+    x[5, 17] = 300.0
+    codes, scales = OQ.fp8_quant_1x128(x)
+    assert codes.shape == (37, 384) and scales.shape == (37, 3)
+    assert torch.all(scales[3] == torch.tensor(1e-4, dtype=torch.float32) * torch.tensor(1 / 448, dtype=torch.float32))
+    assert torch.all(codes[3] == 0)
+    deq = OQ.fp8_dequant_1x128(codes, scales)
+    assert (deq - x.float()).abs().max() <= 0.0625 * x.float().abs().max()
+    # the block maximum always maps to +-448 (0x7E / 0xFE)
+    assert codes[5, 17] == 0x7E
+    # short last block == zero padded block
+    c64, s64 = OQ.fp8_quant_1x128(x[:, :64].contiguous())
+    assert c64.shape == (37, 128) and torch.all(c64[:, 64:] == 0)
+
+
+def test_fp8_128x128_consistent_with_1x128_arithmetic():
+    w = torch.randn(2, 130, 200, generator=torch.Generator().manual_seed(2)).bfloat16()
+    codes, scales = OQ.fp8_quant_128x128(w)
+    assert codes.shape == (2, 130, 256) and scales.shape == (2, 2, 2)
+    blk = w[1, :128, 128:200].float()
+    s = blk.abs().max().clamp_min(1e-4) * torch.tensor(1 / 448, dtype=torch.float32)
+    assert scales[1, 0, 1] == s
+    ref = (blk / s).clamp(-448, 448).to(torch.float8_e4m3fn).view(torch.uint8)
+    assert torch.equal(codes[1, :128, 128:200], ref)
+    deq = OQ.fp8_dequant_128x128(codes, scales)[:, :, :200]
+    assert (deq - w.float()).abs().max() <= 0.0625 * w.float().abs().max()
+
+
+@pytest.mark.parametrize("name", ["uniform", "skew", "hole", "one"])
+def test_layout_oracle_matches_reference(golden, name):
+    g = golden("layout_cases.npz")
+    idx = torch.from_numpy(g[f"{name}_idx"])
+    E = int(g[f"{name}_E"])
+    order, tok, counts = OL.sort_tokens(idx, E)
+    assert np.array_equal(order.numpy(), g[f"{name}_order"])
+    assert np.array_equal(tok.numpy(), g[f"{name}_tok"])
+    assert np.array_equal(counts.numpy(), g[f"{name}_counts"])
+    lay = OL.padded_layout(idx.reshape(-1), E, idx.shape[1])
+    assert lay["P_max"] == int(g[f"{name}_P_max"])
+    assert np.array_equal(lay["pad_pos"].numpy(), g[f"{name}_pad_pos"])
+    assert np.array_equal(lay["tile_e"].numpy(), g[f"{name}_tile_e"])
+    assert np.array_equal(lay["pad_off"][:-1].numpy(), g[f"{name}_seg_start"])
+    assert np.array_equal(lay["pad_off"][1:].numpy(), g[f"{name}_seg_end"])
+    assert np.array_equal(lay["row_of_flat"].numpy(), g[f"{name}_row_of_flat"])
+    assert np.array_equal(lay["counts"].numpy(), g[f"{name}_count_i32"])
+    fof = lay["flat_of_row"].clone()
+    fof[fof < 0] = 0                      # the reference leaves 0 in padding rows
+    assert np.array_equal(fof.numpy(), g[f"{name}_flat_of_row"])
+
+
+def _tiny(golden):
+    g = golden("moe_tiny.npz")
+    t = {k: bf16_from_bits(g[k]) for k in ("x", "w1", "w2", "w3", "shared_out", "y_ref", "y_fast")}
+    t["weights"] = torch.from_numpy(g["route_weights"])
+    t["indices"] = torch.from_numpy(g["route_indices"])
+    t["limit"] = float(g["swiglu_limit"])
+    return t
+
+
+def test_bf16_moe_oracle_matches_reference_forward(golden):
+    t = _tiny(golden)
+    x2 = t["x"].view(-1, t["x"].shape[-1])
+    y = OM.moe_bf16(x2, t["w1"], t["w3"], t["w2"], t["weights"], t["indices"], t["limit"],
+                    shared=t["shared_out"])
+    assert torch.equal(y.view_as(t["y_fast"]), t["y_fast"])
+    mx, mean = OM.rel_errors(y.view_as(t["y_ref"]), t["y_ref"])
+    assert mx <= 1e-2                      # M.MoE.forward sums slots in expert order: last-ulp
+
+
+def test_fp8_moe_oracle_close_to_bf16_reference(golden):
+    t = _tiny(golden)
+    x2 = t["x"].view(-1, t["x"].shape[-1])
+    y = OM.moe_fp8(x2, t["w1"], t["w3"], t["w2"], t["weights"], t["indices"], t["limit"],
+                   shared=t["shared_out"])
+    mx, mean = OM.rel_errors(y.view_as(t["y_ref"]), t["y_ref"])
+    assert mx <= 1e-1 and mean <= 2e-2       # sanity: FP8 quantisation noise vs the bf16 layer
