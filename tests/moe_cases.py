@@ -1,0 +1,30 @@
+"""Seeded synthetic workloads shared by the GPU tests, smoke() and bench.py."""
+from __future__ import annotations
+
+import torch
+
+
+def make_case(T, E, k, D, I, seed=0, zipf=True, outliers=True, empty_expert=None, device="cpu"):
+    """x [T,D], w1/w3 [E,I,D], w2 [E,D,I] bf16 ~ N(0,1) (weights / sqrt(K)), 0.1 % of entries
+    x100; top-k routing without replacement from a Zipf(s=1) or uniform expert popularity;
+    routing weights uniform(0,1) normalised per token and scaled by 1.5."""
+    gen = torch.Generator().manual_seed(seed)
+
+    def rnd(*shape, scale=1.0):
+        t = torch.randn(*shape, generator=gen) * scale
+        if outliers:
+            t = torch.where(torch.rand(*shape, generator=gen) < 0.001, t * 100, t)
+        return t.bfloat16()
+
+    x = rnd(T, D)
+    w1 = rnd(E, I, D, scale=D ** -0.5)
+    w3 = rnd(E, I, D, scale=D ** -0.5)
+    w2 = rnd(E, D, I, scale=I ** -0.5)
+    p = 1.0 / torch.arange(1, E + 1).float() if zipf else torch.ones(E)
+    if empty_expert is not None:
+        p[empty_expert] = 0
+    idx = torch.multinomial(p.expand(T, E), k, replacement=False, generator=gen)
+    w = torch.rand(T, k, generator=gen) + 0.05
+    w = w / w.sum(-1, keepdim=True) * 1.5
+    out = dict(x=x, w1=w1, w3=w3, w2=w2, indices=idx, weights=w.float())
+    return {n: t.to(device) for n, t in out.items()}

@@ -1,0 +1,134 @@
+"""GPU: grouped FP8 GEMMs (tcgen05) and the fused forward through the C ABI vs the
+dequantise-then-fp32-matmul oracle.
+
+Tolerances (bf16 outputs, error normalised by max|ref| as in the reference's
+tests/kernel_parity_fast_moe.py:68-75): max rel <= 2e-2, mean rel <= 2e-3.  Quantised codes and
+scales are compared bit-for-bit.
+"""
+import pytest
+import torch
+
+from moe_cases import make_case
+from oracle import moe as OM
+from oracle import quant as OQ
+
+pytestmark = pytest.mark.gpu
+MAX_REL, MEAN_REL = 2e-2, 2e-3
+LIMIT = 10.0
+
+CASES = {
+    "tiny_c1": dict(T=128, E=4, k=2, D=64, I=128),
+    "d8": dict(T=512, E=8, k=2, D=256, I=256),
+    "d12": dict(T=700, E=16, k=2, D=384, I=384),
+    "c2_small": dict(T=1024, E=8, k=6, D=1024, I=1024),
+    "empty_expert": dict(T=300, E=8, k=2, D=256, I=128, empty_expert=3),
+    "wide": dict(T=256, E=4, k=2, D=2048, I=1024),
+}
+
+
+def _run(case):
+    from nanov41_b200 import ops
+    c = make_case(seed=11, **case)
+    g = {n: t.cuda() for n, t in c.items()}
+    wq = ops.quantize_expert_weights(g["w1"], g["w3"], g["w2"])
+    out, parts = ops.moe_forward_fp8(g["x"], wq, g["weights"], g["indices"], LIMIT,
+                                     return_parts=True)
+    ops.check_status()
+    ref, rparts = OM.moe_fp8(c["x"], c["w1"], c["w3"], c["w2"], c["weights"], c["indices"],
+                             LIMIT, return_parts=True)
+    return c, wq, out, parts, ref, rparts
+
+
+@pytest.mark.parametrize("name", list(CASES))
+def test_forward_fp8_vs_oracle(name):
+    from nanov41_b200 import ops
+    c, wq, out, parts, ref, rp = _run(CASES[name])
+    lay = parts["layout"]
+    D, I = c["x"].shape[1], c["w1"].shape[1]
+    # quantised inputs: bit exact
+    assert torch.equal(parts["x_codes"].cpu(), rp["x_codes"])
+    assert torch.equal(parts["x_scale"].cpu(), rp["x_scales"].t().contiguous())
+    assert torch.equal(wq.w13_codes.cpu(), rp["w13"][0]) and torch.equal(wq.w13_scale.cpu(), rp["w13"][1])
+    assert torch.equal(wq.w2_codes.cpu(), rp["w2"][0]) and torch.equal(wq.w2_scale.cpu(), rp["w2"][1])
+    pad_pos = lay.pad_pos.cpu().long()           # sorted position -> padded row
+    gate, up, h = (parts[n].cpu()[pad_pos] for n in ("gate", "up", "h"))
+    for got, want, nm in ((gate, rp["gate"], "gate"), (up, rp["up"], "up"), (h, rp["h"], "h")):
+        mx, mean = OM.rel_errors(got, want)
+        assert mx <= 8e-3 and mean <= 5e-4, (nm, mx, mean)
+    # padding rows of the padded space are exact zeros
+    padmask = lay.row_token.cpu() < 0
+    used = int(lay.meta[1].item())
+    assert torch.all(parts["h"].cpu()[:used][padmask[:used]] == 0)
+    # the fused epilogue quantizer: codes/scales of OUR h, bit exact vs act_quant of that h
+    hc, hs = OQ.fp8_quant_1x128(parts["h"].cpu()[:used])
+    assert torch.equal(parts["h_codes"].cpu()[:used], hc)
+    assert torch.equal(parts["h_scale"].cpu()[:, :used], hs.t().contiguous())
+    # down projection and the combined output
+    mx, mean = OM.rel_errors(parts["y_rows"].cpu()[pad_pos], rp["outs"])
+    assert mx <= MAX_REL and mean <= MEAN_REL, ("y_rows", mx, mean)
+    mx, mean = OM.rel_errors(out.cpu(), ref)
+    assert mx <= MAX_REL and mean <= MEAN_REL, ("out", mx, mean)
+
+
+def test_contiguous_and_gathered_activations_agree():
+    from nanov41_b200 import ops
+    c = make_case(seed=5, **CASES["d12"])
+    g = {n: t.cuda() for n, t in c.items()}
+    wq = ops.quantize_expert_weights(g["w1"], g["w3"], g["w2"])
+    lay = ops.build_layout(g["indices"].reshape(-1), wq.E, 2, g["weights"].reshape(-1))
+    xc, xs = ops.quant_fp8_1x128(g["x"], scale_kmajor=True)
+    a = ops.gemm1_fp8(ops.A_GATHER_FP8, xc, xs, wq.w13_codes, wq.w13_scale, lay, LIMIT, True, True)
+    xpc, xps = ops.quant_fp8_1x128(g["x"], gather=lay.row_token, scale_kmajor=True)
+    b = ops.gemm1_fp8(ops.A_CONTIGUOUS, xpc, xps, wq.w13_codes, wq.w13_scale, lay, LIMIT, True, True)
+    ops.check_status()
+    used = int(lay.meta[1].item())
+    for ta, tb in zip(a, b):
+        if ta.shape[0] == lay.P_max:
+            assert torch.equal(ta[:used], tb[:used])
+        else:
+            assert torch.equal(ta[:, :used], tb[:, :used])
+
+
+def test_forward_is_deterministic():
+    from nanov41_b200 import ops
+    c = make_case(seed=3, **CASES["d8"])
+    g = {n: t.cuda() for n, t in c.items()}
+    wq = ops.quantize_expert_weights(g["w1"], g["w3"], g["w2"])
+    a = ops.moe_forward_fp8(g["x"], wq, g["weights"], g["indices"], LIMIT)
+    b = ops.moe_forward_fp8(g["x"], wq, g["weights"], g["indices"], LIMIT)
+    assert torch.equal(a, b)
+
+
+def test_full_size_c2_spot_check():
+    """BASELINE config 2 at full size (E=64, T=16384, k=6, D=I=1024): the three least-loaded
+    experts are checked row by row against the oracle; the whole output through finiteness and
+    the linearity of the combine (sum over tokens of out == sum over rows of y_rows)."""
+    from nanov41_b200 import ops
+    c = make_case(T=16384, E=64, k=6, D=1024, I=1024, seed=1)
+    g = {n: t.cuda() for n, t in c.items()}
+    wq = ops.quantize_expert_weights(g["w1"], g["w3"], g["w2"])
+    out, parts = ops.moe_forward_fp8(g["x"], wq, g["weights"], g["indices"], LIMIT,
+                                     return_parts=True)
+    ops.check_status()
+    assert torch.isfinite(out.float()).all()
+    lay = parts["layout"]
+    counts = lay.counts.cpu()
+    pad_off = lay.pad_off.cpu()
+    xd = OQ.fp8_dequant_1x128(*OQ.fp8_quant_1x128(c["x"]))
+    for e in torch.argsort(counts)[:3].tolist():
+        n, p0 = int(counts[e]), int(pad_off[e])
+        tok = lay.row_token[p0:p0 + n].cpu().long()
+        wr = lay.row_weight[p0:p0 + n].cpu()
+        (c13, s13), (c2, s2) = OM.quantize_weights_fp8(c["w1"][e:e + 1], c["w3"][e:e + 1], c["w2"][e:e + 1])
+        w13d = OQ.fp8_dequant_128x128(c13, s13)[0]
+        w2d = OQ.fp8_dequant_128x128(c2, s2)[0]
+        gu = (xd[tok] @ w13d.t()).bfloat16()
+        h = OM.swiglu(gu[:, :1024].float(), gu[:, 1024:].float(), LIMIT, wr[:, None]).bfloat16()
+        hd = OQ.fp8_dequant_1x128(*OQ.fp8_quant_1x128(h))
+        y = (hd @ w2d.t()).bfloat16()
+        mx, mean = OM.rel_errors(parts["y_rows"][p0:p0 + n].cpu(), y)
+        assert mx <= MAX_REL and mean <= MEAN_REL, (e, mx, mean)
+    used = int(lay.meta[1].item())
+    rows_sum = parts["y_rows"][:used].float()[lay.row_token[:used] >= 0].sum(0)
+    tok_sum = out.float().sum(0)
+    assert torch.allclose(rows_sum, tok_sum, rtol=0, atol=2e-2 * rows_sum.abs().max().item() + 4.0)

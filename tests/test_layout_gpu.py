@@ -1,0 +1,85 @@
+"""GPU: router-sorted layout and top-k combine through the C ABI, bit-exact vs the oracle and
+the reference fixtures."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import layout as OL
+
+pytestmark = pytest.mark.gpu
+
+
+def _check(idx, E, k, weights=None):
+    from nanov41_b200 import ops
+    lay = ops.build_layout(idx.reshape(-1).cuda(), E, k,
+                           None if weights is None else weights.reshape(-1).cuda())
+    ref = OL.padded_layout(idx.reshape(-1), E, k)
+    assert lay.P_max == ref["P_max"]
+    assert int(lay.status.item()) == 0
+    for name in ("counts", "order", "pad_pos", "row_of_flat", "flat_of_row"):
+        assert torch.equal(getattr(lay, name).cpu().long(), ref[name]), name
+    assert torch.equal(lay.pad_off.cpu().long(), ref["pad_off"])
+    assert torch.equal(lay.cum_excl.cpu().long(), ref["cum_excl"])
+    assert torch.equal(lay.tile_expert.cpu().long(), ref["tile_e"])
+    tok = torch.full((ref["P_max"],), -1, dtype=torch.int64)
+    tok[ref["pad_pos"]] = ref["tok"]
+    assert torch.equal(lay.row_token.cpu().long(), tok)
+    meta = lay.meta.cpu().tolist()
+    assert meta == [int(ref["pad_off"][-1]) // 128, int(ref["pad_off"][-1]), idx.numel(), E]
+    if weights is not None:
+        rw = torch.zeros(ref["P_max"])
+        rw[ref["row_of_flat"]] = weights.reshape(-1).float()
+        assert torch.equal(lay.row_weight.cpu(), rw)
+    return lay
+
+
+@pytest.mark.parametrize("name", ["uniform", "skew", "hole", "one"])
+def test_layout_matches_reference_fixture(golden, name):
+    g = golden("layout_cases.npz")
+    idx = torch.from_numpy(g[f"{name}_idx"])
+    lay = _check(idx, int(g[f"{name}_E"]), idx.shape[1])
+    assert np.array_equal(lay.order.cpu().numpy(), g[f"{name}_order"])
+    assert np.array_equal(lay.pad_pos.cpu().numpy(), g[f"{name}_pad_pos"])
+    assert np.array_equal(lay.tile_expert.cpu().numpy(), g[f"{name}_tile_e"])
+    assert np.array_equal(lay.row_of_flat.cpu().numpy(), g[f"{name}_row_of_flat"])
+
+
+@pytest.mark.parametrize("T,E,k,seed", [(16384, 64, 6, 1), (1000, 256, 8, 2), (3, 4, 2, 0),
+                                        (4096, 16, 2, 3), (50000, 8, 1, 4)])
+def test_layout_random(T, E, k, seed):
+    gen = torch.Generator().manual_seed(seed)
+    p = 1.0 / torch.arange(1, E + 1).float()
+    idx = torch.multinomial(p.expand(T, E), k, replacement=False, generator=gen)
+    w = torch.rand(T, k, generator=gen)
+    _check(idx, E, k, w)
+    _check(idx.int(), E, k)
+
+
+def test_layout_all_rows_one_expert_and_out_of_range():
+    from nanov41_b200 import ops
+    idx = torch.full((300, 1), 2, dtype=torch.int64)
+    _check(idx, 4, 1)
+    bad = idx.clone()
+    bad[7] = 9
+    lay = ops.build_layout(bad.reshape(-1).cuda(), 4, 1)
+    assert int(lay.status.item()) == 1
+
+
+@pytest.mark.parametrize("T,k,D,shared", [(128, 2, 64, True), (1000, 6, 1024, False), (77, 8, 2048, True)])
+def test_combine_bit_exact(T, k, D, shared):
+    from nanov41_b200 import ops
+    gen = torch.Generator().manual_seed(T)
+    E = 8
+    idx = torch.stack([torch.randperm(E, generator=gen)[:k] for _ in range(T)])
+    ref = OL.padded_layout(idx.reshape(-1), E, k)
+    y = torch.randn(ref["P_max"], D, generator=gen).bfloat16()
+    sh = torch.randn(T, D, generator=gen).bfloat16() if shared else None
+    out = ops.combine(y.cuda(), ref["row_of_flat"].int().cuda(), T, k,
+                      None if sh is None else sh.cuda())
+    acc = torch.zeros(T, D)
+    rows = ref["row_of_flat"].view(T, k)
+    for j in range(k):
+        acc = acc + y[rows[:, j]].float()
+    if sh is not None:
+        acc = acc + sh.float()
+    assert torch.equal(out.cpu(), acc.bfloat16())

@@ -1,0 +1,105 @@
+"""GPU: quantizer kernels through the C ABI, bit-exact against the oracle."""
+import numpy as np
+import pytest
+import torch
+
+from conftest import bf16_from_bits
+from oracle import quant as OQ
+
+pytestmark = pytest.mark.gpu
+
+
+def _ops():
+    from nanov41_b200 import ops
+    return ops
+
+
+def _x(rows, k, seed, outliers=False, mul=1.0):
+    gen = torch.Generator().manual_seed(seed)
+    x = torch.randn(rows, k, generator=gen) * mul
+    if outliers:
+        mask = torch.rand(rows, k, generator=gen) < 0.001
+        x = torch.where(mask, x * 100, x)
+    return x.bfloat16()
+
+
+@pytest.mark.parametrize("rows,k,outliers", [(128, 64, False), (1, 128, False), (257, 384, True),
+                                             (1000, 1024, True), (33, 2048, False), (5, 200, False)])
+def test_fp8_1x128_bit_exact(rows, k, outliers):
+    ops = _ops()
+    x = _x(rows, k, rows + k, outliers)
+    x[0] = 0
+    codes, scales = ops.quant_fp8_1x128(x.cuda())
+    oc, osc = OQ.fp8_quant_1x128(x)
+    assert torch.equal(scales.cpu().view(torch.int32), osc.view(torch.int32))
+    assert torch.equal(codes.cpu(), oc)
+
+
+def test_fp8_1x128_kmajor_scales_and_gather():
+    ops = _ops()
+    x = _x(300, 256, 7, True)
+    gather = torch.randint(0, 300, (512,), generator=torch.Generator().manual_seed(1)).int()
+    gather[5] = -1
+    gather[511] = -1
+    codes, scales = ops.quant_fp8_1x128(x.cuda(), gather=gather.cuda(), scale_kmajor=True)
+    src = x[gather.clamp_min(0).long()].clone()
+    src[gather < 0] = 0
+    oc, osc = OQ.fp8_quant_1x128(src)
+    assert torch.equal(codes.cpu(), oc)
+    assert torch.equal(scales.cpu(), osc.t().contiguous())
+
+
+def test_fp8_1x128_strided_rows_and_empty():
+    ops = _ops()
+    big = _x(64, 512, 3).cuda()
+    view = big[:, 128:384]
+    codes, scales = ops.quant_fp8_1x128(view)
+    oc, osc = OQ.fp8_quant_1x128(view.cpu().contiguous())
+    assert torch.equal(codes.cpu(), oc) and torch.equal(scales.cpu(), osc)
+    c0, s0 = ops.quant_fp8_1x128(big[:0])
+    assert c0.shape == (0, 512) and s0.shape == (0, 4)
+
+
+@pytest.mark.parametrize("E,N,K", [(4, 256, 64), (3, 128, 128), (2, 64, 128), (2, 384, 384),
+                                   (2, 200, 328), (8, 2048, 1024)])
+def test_fp8_128x128_bit_exact(E, N, K):
+    ops = _ops()
+    gen = torch.Generator().manual_seed(E * N + K)
+    w = (torch.randn(E, N, K, generator=gen) / K ** 0.5).bfloat16()
+    w[0, : min(N, 128), : min(K, 128)] = 0          # an all-zero block
+    codes, scales, codes_t = ops.quant_fp8_128x128(w.cuda(), transposed=True)
+    oc, osc = OQ.fp8_quant_128x128(w)
+    assert torch.equal(scales.cpu().view(torch.int32), osc.view(torch.int32))
+    assert torch.equal(codes.cpu(), oc)
+    npad = (N + 127) // 128 * 128
+    ref_t = torch.zeros(E, oc.shape[2], npad, dtype=torch.uint8)
+    ref_t[:, :, :N] = oc.transpose(1, 2)
+    assert torch.equal(codes_t.cpu(), ref_t)
+
+
+@pytest.mark.parametrize("name", ["c0", "c1", "c2", "c3", "c4", "c5", "ties", "zeros"])
+def test_nvfp4_bit_exact_vs_reference_fixture(golden, name):
+    ops = _ops()
+    g = golden("nvfp4_cases.npz")
+    x = bf16_from_bits(g[f"{name}_x"])
+    packed, sbytes = ops.quant_nvfp4_1x16(x.cuda())
+    assert np.array_equal(packed.cpu().numpy(), g[f"{name}_packed"])
+    assert np.array_equal(sbytes.cpu().numpy(), g[f"{name}_scale"])
+
+
+@pytest.mark.parametrize("rows,k,gs,dtype", [(1152, 384, 1.0, torch.bfloat16),
+                                             (777, 1024, 0.013, torch.bfloat16),
+                                             (64, 64, 3.7e-4, torch.float32)])
+def test_nvfp4_bit_exact_vs_oracle(rows, k, gs, dtype):
+    ops = _ops()
+    x = (torch.randn(rows, k, generator=torch.Generator().manual_seed(rows)) * 0.02).to(dtype)
+    packed, sbytes = ops.quant_nvfp4_1x16(x.cuda(), gs)
+    op, osb = OQ.nvfp4_quant(x, gs)
+    assert torch.equal(sbytes.cpu(), osb)
+    assert torch.equal(packed.cpu(), op)
+
+
+def test_cpu_tensor_is_rejected():
+    ops = _ops()
+    with pytest.raises(RuntimeError):
+        ops.quant_fp8_1x128(torch.zeros(4, 128, dtype=torch.bfloat16))
