@@ -14,14 +14,14 @@
 // Pipeline per CTA (512 threads):
 //   warp 0      TMA producer: weight tiles (and activation tiles when they are contiguous)
 //   warp 1      UMMA issuer (one thread) + TMEM allocation
-//   warps 4-7   activation producers for the gathered modes: fetch the rows of the tile by
-//               token index (fp8 codes, or bf16 rows that are quantised 1x128 on the fly) and
-//               write them into the 128-byte-swizzled stage
-//   warps 8-15  promotion + epilogue: every 128-wide K block is read back from TMEM
-//               (tcgen05.ld) and folded into fp32 registers with sa[row] * sw[n-block]
-//               (the scales are arbitrary fp32, so the hardware block-scaled kinds, which take
-//               power-of-two ue8m0 scales, do not apply), then SwiGLU + re-quantisation or a
-//               bf16 store.
+//   warps 2-3   activation producers for the gathered mode: fetch the rows of the tile by
+//               token index and write them into the 128-byte-swizzled stage
+//   warps 8-15  promotion: every 128-wide K block is read back from TMEM (tcgen05.ld) and
+//               folded into fp32 registers with sa[row] * sw[n-block] (the scales are arbitrary
+//               fp32, so the hardware block-scaled kinds, which take power-of-two ue8m0 scales,
+//               do not apply); at the end of a tile either a bf16 store, or the bf16 gate|up
+//               tile is handed through shared memory to
+//   warps 4-7   SwiGLU + 1x128 re-quantisation of h + stores, which overlap the next tile.
 // TMEM holds two 256-column accumulator buffers, so the UMMAs of K block i+1 overlap the
 // promotion of K block i.  Every mbarrier wait is bounded and reports through `status`.
 #include <cuda.h>
@@ -39,10 +39,10 @@ namespace nv41 {
 constexpr int kBM = 128;                 // tile rows
 constexpr int kBK = 128;                 // K per stage = one scale block = one swizzle row
 constexpr int kBN = 256;                 // UMMA N (two 128-row weight boxes)
-constexpr int kStages = 4;
 constexpr int kABytes = kBM * kBK;       // 16 KiB
 constexpr int kBBytes = kBN * kBK;       // 32 KiB
 constexpr int kStageBytes = kABytes + kBBytes;
+constexpr int kHandBytes = kBM * kBN * 2;  // bf16 gate|up tile handed to the SwiGLU warps
 constexpr int kThreads = 512;
 constexpr int kTmemCols = 512;
 
@@ -81,53 +81,67 @@ struct GemmArgs {
   uint32_t* status;
 };
 
+// Shared-memory carve-up.  NS stages of (A 16 KiB | B 32 KiB), then (SwiGLU only) the 64 KiB
+// hand-off tile, then barriers and small scratch.
+template <int NS, bool HAND>
 struct Smem {
   uint8_t* base;
   __device__ uint8_t* a(int s) const { return base + s * kStageBytes; }
   __device__ uint8_t* b(int s) const { return base + s * kStageBytes + kABytes; }
+  __device__ uint8_t* hand() const { return base + NS * kStageBytes; }
   __device__ uint64_t* bars() const {
-    return reinterpret_cast<uint64_t*>(base + kStages * kStageBytes);
+    return reinterpret_cast<uint64_t*>(base + NS * kStageBytes + (HAND ? kHandBytes : 0));
   }
   __device__ uint64_t* full(int s) const { return bars() + s; }
-  __device__ uint64_t* empty(int s) const { return bars() + kStages + s; }
-  __device__ uint64_t* tfull(int b) const { return bars() + 2 * kStages + b; }
-  __device__ uint64_t* tempty(int b) const { return bars() + 2 * kStages + 2 + b; }
-  __device__ uint64_t* xbar(int b) const { return bars() + 2 * kStages + 4 + b; }
+  __device__ uint64_t* empty(int s) const { return bars() + NS + s; }
+  __device__ uint64_t* tfull(int b) const { return bars() + 2 * NS + b; }
+  __device__ uint64_t* tempty(int b) const { return bars() + 2 * NS + 2 + b; }
+  __device__ uint64_t* hfull() const { return bars() + 2 * NS + 4; }
+  __device__ uint64_t* hempty() const { return bars() + 2 * NS + 5; }
   __device__ uint32_t* tmem_slot() const {
-    return reinterpret_cast<uint32_t*>(bars() + 2 * kStages + 6);
+    return reinterpret_cast<uint32_t*>(bars() + 2 * NS + 6);
   }
   __device__ volatile uint32_t* abort_flag() const { return tmem_slot() + 1; }
-  __device__ float* xch() const { return reinterpret_cast<float*>(tmem_slot() + 4); }  // [2][2][128]
+  __device__ int* gather_tok() const { return reinterpret_cast<int*>(tmem_slot() + 4); }  // [2][64]
+  static constexpr int kBytes =
+      NS * kStageBytes + (HAND ? kHandBytes : 0) + (2 * NS + 6) * 8 + 16 + 2 * 64 * 4 + 1024;
 };
-constexpr int kSmemTail = (2 * kStages + 6) * 8 + 16 + 2 * 2 * 128 * 4;
-constexpr int kSmemBytes = kStages * kStageBytes + kSmemTail + 1024;  // +1024: manual alignment
 
-__device__ __forceinline__ float bf16_round(float x) {
-  return __bfloat162float(__float2bfloat16_rn(x));
-}
 __device__ __forceinline__ uint32_t pack_bf16x2(float a, float b) {
   const __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
   return *reinterpret_cast<const uint32_t*>(&v);
 }
-__device__ __forceinline__ uint32_t e4m3x4(float a, float b, float c, float d, float s) {
-  const float q0 = fminf(fmaxf(__fdiv_rn(a, s), -448.f), 448.f);
-  const float q1 = fminf(fmaxf(__fdiv_rn(b, s), -448.f), 448.f);
-  const float q2 = fminf(fmaxf(__fdiv_rn(c, s), -448.f), 448.f);
-  const float q3 = fminf(fmaxf(__fdiv_rn(d, s), -448.f), 448.f);
-  const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(q0, q1), __NV_SATFINITE, __NV_E4M3);
-  const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(q2, q3), __NV_SATFINITE, __NV_E4M3);
+__device__ __forceinline__ float bf16_lo(uint32_t w) { return __uint_as_float(w << 16); }
+__device__ __forceinline__ float bf16_hi(uint32_t w) { return __uint_as_float(w & 0xFFFF0000u); }
+
+// Correctly rounded a / s from r = RN(1 / s): two FMA correction steps (no special cases are
+// needed for the operand range of the quantizer: s >= 1e-4/448, |a / s| <= 448 (1 + eps)).
+__device__ __forceinline__ float div_by_scale(float a, float s, float r) {
+  float q = a * r;
+  float e = fmaf(-s, q, a);
+  q = fmaf(e, r, q);
+  e = fmaf(-s, q, a);
+  return copysignf(fmaf(e, r, q), a);   // keeps -0.0 (code 0x80), which the FMA chain loses
+}
+// e4m3 codes (round-to-nearest-even, saturating at +-448) of four quotients
+__device__ __forceinline__ uint32_t e4m3x4(float a, float b, float c, float d, float s, float r) {
+  const uint32_t lo = __nv_cvt_float2_to_fp8x2(
+      make_float2(div_by_scale(a, s, r), div_by_scale(b, s, r)), __NV_SATFINITE, __NV_E4M3);
+  const uint32_t hi = __nv_cvt_float2_to_fp8x2(
+      make_float2(div_by_scale(c, s, r), div_by_scale(d, s, r)), __NV_SATFINITE, __NV_E4M3);
   return lo | (hi << 16);
 }
 
+#define NV41_FOR_EACH_UNIT(g, mt, nt, e)                                   \
+  for (int w_ = blockIdx.x, total_ = (g).n_tiles_m * (g).n_tiles_n, mt = 0, nt = 0, e = 0; \
+       w_ < total_; w_ += gridDim.x)                                       \
+    if ((mt = w_ / (g).n_tiles_n, nt = w_ - mt * (g).n_tiles_n, e = (g).tile_expert[mt]) >= 0)
+
 // ------------------------------------------------------------------------------ TMA warp
-template <int MODE_A, int EPI>
-__device__ __forceinline__ void role_tma(const GemmArgs& g, const Smem& sm) {
+template <int MODE_A, int EPI, class SM>
+__device__ __forceinline__ void role_tma(const GemmArgs& g, const SM& sm, int NS) {
   uint32_t it = 0;
-  const int total = g.n_tiles_m * g.n_tiles_n;
-  for (int w = blockIdx.x; w < total; w += gridDim.x) {
-    const int mt = w / g.n_tiles_n, nt = w - mt * g.n_tiles_n;
-    const int e = g.tile_expert[mt];
-    if (e < 0) continue;
+  NV41_FOR_EACH_UNIT(g, mt, nt, e) {
     int brow0, brow1;
     if (EPI == EPI_SWIGLU) {
       brow0 = e * g.b_rows_per_expert + nt * 128;
@@ -137,8 +151,8 @@ __device__ __forceinline__ void role_tma(const GemmArgs& g, const Smem& sm) {
       brow1 = brow0 + 128;
     }
     for (int kb = 0; kb < g.nkb; ++kb, ++it) {
-      const int s = it % kStages;
-      const uint32_t ph = (it / kStages) & 1u;
+      const int s = it % NS;
+      const uint32_t ph = (it / NS) & 1u;
       if (!mbar_wait(sm.empty(s), ph ^ 1u, sm.abort_flag(), g.status, ST_TIMEOUT_EMPTY)) return;
       const uint32_t bytes = kBBytes + (MODE_A == A_TMA ? kABytes : 0);
       mbar_arrive_expect_tx(sm.full(s), bytes);
@@ -150,16 +164,15 @@ __device__ __forceinline__ void role_tma(const GemmArgs& g, const Smem& sm) {
 }
 
 // ------------------------------------------------------------------------------ UMMA warp
-__device__ __forceinline__ void role_mma(const GemmArgs& g, const Smem& sm, uint32_t tmem_base) {
+template <class SM>
+__device__ __forceinline__ void role_mma(const GemmArgs& g, const SM& sm, uint32_t tmem_base,
+                                         int NS) {
   constexpr uint32_t idesc = umma_idesc(kBM, kBN, 0, 0);
   uint32_t it = 0;
-  const int total = g.n_tiles_m * g.n_tiles_n;
-  for (int w = blockIdx.x; w < total; w += gridDim.x) {
-    const int mt = w / g.n_tiles_n;
-    if (g.tile_expert[mt] < 0) continue;
+  NV41_FOR_EACH_UNIT(g, mt, nt, e) {
     for (int kb = 0; kb < g.nkb; ++kb, ++it) {
-      const int s = it % kStages;
-      const uint32_t ph = (it / kStages) & 1u;
+      const int s = it % NS;
+      const uint32_t ph = (it / NS) & 1u;
       const uint32_t b = it & 1u, tph = (it >> 1) & 1u;
       if (!mbar_wait(sm.full(s), ph, sm.abort_flag(), g.status, ST_TIMEOUT_FULL)) return;
       if (!mbar_wait(sm.tempty(b), tph ^ 1u, sm.abort_flag(), g.status, ST_TIMEOUT_TMEM_EMPTY))
@@ -178,59 +191,78 @@ __device__ __forceinline__ void role_mma(const GemmArgs& g, const Smem& sm, uint
 }
 
 // ------------------------------------------------------------------------------ A producers
-// 4 warps; lane -> 16-byte chunk (lane & 7) of rows (lane >> 3) + 4 i of the warp's 32 rows.
-template <int MODE_A>
-__device__ __forceinline__ void role_gather(const GemmArgs& g, const Smem& sm, int pw, int lane) {
+// 2 warps x 64 rows; lane -> 16-byte chunk (lane & 7) of rows (lane >> 3) + 4 i.  The rows are
+// copied global -> shared with cp.async (zero-filled for padding rows); the copies of K block
+// i+1 are issued before the warp waits for those of K block i, so two blocks are in flight.
+__device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src, uint32_t src_bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src),
+               "r"(src_bytes)
+               : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() {
+  asm volatile("cp.async.commit_group;" ::: "memory");
+}
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+template <int MODE_A, class SM>
+__device__ __forceinline__ void role_gather(const GemmArgs& g, const SM& sm, int gw, int lane,
+                                            int NS) {
   uint32_t it = 0;
-  const int total = g.n_tiles_m * g.n_tiles_n;
-  const int c = lane & 7;
-  for (int w = blockIdx.x; w < total; w += gridDim.x) {
-    const int mt = w / g.n_tiles_n;
-    if (g.tile_expert[mt] < 0) continue;
-    int tok[8];
-#pragma unroll
-    for (int i = 0; i < 8; ++i) tok[i] = g.row_token[mt * kBM + pw * 32 + i * 4 + (lane >> 3)];
+  const int c = lane & 7, rsub = lane >> 3;
+  int* tokbuf = sm.gather_tok() + gw * 64;
+  int pending = -1;                      // stage whose copies are in flight, not yet published
+  NV41_FOR_EACH_UNIT(g, mt, nt, e) {
+    __syncwarp();
+    tokbuf[lane] = g.row_token[mt * kBM + gw * 64 + lane];
+    tokbuf[lane + 32] = g.row_token[mt * kBM + gw * 64 + 32 + lane];
+    __syncwarp();
     for (int kb = 0; kb < g.nkb; ++kb, ++it) {
-      const int s = it % kStages;
-      const uint32_t ph = (it / kStages) & 1u;
+      const int s = it % NS;
+      const uint32_t ph = (it / NS) & 1u;
       if (!mbar_wait(sm.empty(s), ph ^ 1u, sm.abort_flag(), g.status, ST_TIMEOUT_EMPTY)) return;
-      uint8_t* dst = sm.a(s);
-      if (MODE_A == A_GATHER_FP8) {
-        uint4 v[8];
+      const uint32_t dst = smem_u32(sm.a(s));
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          v[i] = make_uint4(0u, 0u, 0u, 0u);
-          if (tok[i] >= 0)
-            v[i] = __ldg(reinterpret_cast<const uint4*>(g.a_codes + tok[i] * g.a_ld + kb * kBK +
-                                                        c * 16));
-        }
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const int r = pw * 32 + i * 4 + (lane >> 3);
-          *reinterpret_cast<uint4*>(dst + r * 128 + ((c ^ (r & 7)) << 4)) = v[i];
-        }
+      for (int i = 0; i < 16; ++i) {
+        const int rl = i * 4 + rsub;
+        const int r = gw * 64 + rl;
+        const int tok = tokbuf[rl];
+        const uint8_t* src = g.a_codes + (tok >= 0 ? tok : 0) * g.a_ld + kb * kBK + c * 16;
+        cp_async_16(dst + r * 128 + ((c ^ (r & 7)) << 4), src, tok >= 0 ? 16u : 0u);
       }
-      fence_proxy_async_smem();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(sm.full(s));
+      cp_async_commit();
+      if (pending >= 0) {
+        cp_async_wait<1>();              // everything but the newest group has landed
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(sm.full(pending));
+      }
+      pending = s;
     }
+  }
+  if (pending >= 0) {
+    cp_async_wait<0>();
+    fence_proxy_async_smem();
+    __syncwarp();
+    if (lane == 0) mbar_arrive(sm.full(pending));
   }
 }
 
-// ------------------------------------------------------------------------------ epilogue
-template <int MODE_A, int EPI>
-__device__ __forceinline__ void role_epilogue(const GemmArgs& g, const Smem& sm,
-                                              uint32_t tmem_base, int ew, int lane) {
+// ------------------------------------------------------------------------------ promotion
+// 8 warps.  Thread = (row = TMEM lane, column half).  Per 128-wide K block the 128 fp32 partial
+// sums of the thread are pulled from TMEM in 16-column pieces (the next piece is in flight
+// while the current one is folded into the accumulators).
+template <int MODE_A, int EPI, class SM>
+__device__ __forceinline__ void role_promote(const GemmArgs& g, const SM& sm, uint32_t tmem_base,
+                                             int ew, int lane) {
   const int q = ew & 3;            // TMEM lane quarter this warp may read
   const int half = ew >> 2;        // which half of the tile's columns
   const int row_in_tile = q * 32 + lane;
   const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
   uint32_t it = 0, unit = 0;
-  const int total = g.n_tiles_m * g.n_tiles_n;
-  for (int w = blockIdx.x; w < total; w += gridDim.x) {
-    const int mt = w / g.n_tiles_n, nt = w - mt * g.n_tiles_n;
-    const int e = g.tile_expert[mt];
-    if (e < 0) continue;
+  NV41_FOR_EACH_UNIT(g, mt, nt, e) {
     const long long grow = static_cast<long long>(mt) * kBM + row_in_tile;
     long long sa_idx = grow;
     bool sa_ok = true;
@@ -267,86 +299,56 @@ __device__ __forceinline__ void role_epilogue(const GemmArgs& g, const Smem& sm,
       if (!mbar_wait(sm.tfull(b), tph, sm.abort_flag(), g.status, ST_TIMEOUT_TMEM_FULL)) return;
       tc_fence_after_sync();
       const uint32_t tb = lane_base + b * kBN;
+      // piece c (16 columns): SwiGLU -> gate columns half*64 + 16c (c < 4), up columns
+      // 128 + half*64 + 16(c-4); store -> columns half*128 + 16c
+      auto col = [&](int c) -> uint32_t {
+        return (EPI == EPI_SWIGLU) ? static_cast<uint32_t>((c >> 2) * 128 + half * 64 + (c & 3) * 16)
+                                   : static_cast<uint32_t>(half * 128 + c * 16);
+      };
+      uint32_t va[16], vb[16];
+      tmem_ld_32x32b_x16(tb + col(0), va);
 #pragma unroll
-      for (int ch = 0; ch < 4; ++ch) {
-        // EPI_SWIGLU: chunks 0,1 = gate columns half*64 + {0,32}; 2,3 = up columns (+128)
-        // EPI_STORE : chunks 0..3 = columns half*128 + 32*ch
-        const int col = (EPI == EPI_SWIGLU) ? ((ch >> 1) * 128 + half * 64 + (ch & 1) * 32)
-                                            : (half * 128 + ch * 32);
-        const float f = (EPI == EPI_SWIGLU) ? ((ch >> 1) ? f1 : f0) : f0;
-        uint32_t v[32];
-        tmem_ld_32x32b_x32(tb + col, v);
-        tmem_ld_wait();
+      for (int c = 0; c < 8; c += 2) {
+        const float fa = (EPI == EPI_SWIGLU && c >= 4) ? f1 : f0;
+        tmem_ld_wait_x16(va);
+        tmem_ld_32x32b_x16(tb + col(c + 1), vb);
 #pragma unroll
-        for (int i = 0; i < 32; ++i)
-          acc[ch * 32 + i] = fmaf(__uint_as_float(v[i]), f, acc[ch * 32 + i]);
+        for (int i = 0; i < 16; ++i)
+          acc[c * 16 + i] = fmaf(__uint_as_float(va[i]), fa, acc[c * 16 + i]);
+        tmem_ld_wait_x16(vb);
+        if (c + 2 < 8) {
+          tmem_ld_32x32b_x16(tb + col(c + 2), va);
+        } else {
+          // every piece of this buffer is in registers: hand it back to the UMMA warp
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(sm.tempty(b));
+        }
+#pragma unroll
+        for (int i = 0; i < 16; ++i)
+          acc[(c + 1) * 16 + i] = fmaf(__uint_as_float(vb[i]), fa, acc[(c + 1) * 16 + i]);
       }
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(sm.tempty(b));
     }
 
     if (EPI == EPI_SWIGLU) {
-      // acc[0..63] = gate, acc[64..127] = up for h columns nt*128 + half*64 + i
-      const float wr = g.row_weight[grow];
-      const float L = g.limit;
-      const long long ocol = static_cast<long long>(nt) * 128 + half * 64;
-      if (g.gate_out) {
-#pragma unroll
-        for (int i = 0; i < 64; i += 8) {
-          uint4 vg, vu;
-          vg.x = pack_bf16x2(acc[i], acc[i + 1]);     vg.y = pack_bf16x2(acc[i + 2], acc[i + 3]);
-          vg.z = pack_bf16x2(acc[i + 4], acc[i + 5]); vg.w = pack_bf16x2(acc[i + 6], acc[i + 7]);
-          vu.x = pack_bf16x2(acc[64 + i], acc[65 + i]); vu.y = pack_bf16x2(acc[66 + i], acc[67 + i]);
-          vu.z = pack_bf16x2(acc[68 + i], acc[69 + i]); vu.w = pack_bf16x2(acc[70 + i], acc[71 + i]);
-          *reinterpret_cast<uint4*>(g.gate_out + grow * g.N + ocol + i) = vg;
-          *reinterpret_cast<uint4*>(g.up_out + grow * g.N + ocol + i) = vu;
-        }
-      }
-      float amax = 0.f;
-#pragma unroll
-      for (int i = 0; i < 64; ++i) {
-        float gt = bf16_round(acc[i]);          // Linear output is bf16, then .float()
-        float up = bf16_round(acc[64 + i]);
-        if (L > 0.f) {
-          up = fminf(fmaxf(up, -L), L);
-          gt = fminf(gt, L);
-        }
-        const float sl = __fdividef(gt, 1.f + __expf(-gt));
-        const float hv = bf16_round((sl * up) * wr);
-        acc[i] = hv;
-        amax = fmaxf(amax, fabsf(hv));
-      }
-      if (g.h_out) {
-#pragma unroll
-        for (int i = 0; i < 64; i += 8) {
-          uint4 vh;
-          vh.x = pack_bf16x2(acc[i], acc[i + 1]);     vh.y = pack_bf16x2(acc[i + 2], acc[i + 3]);
-          vh.z = pack_bf16x2(acc[i + 4], acc[i + 5]); vh.w = pack_bf16x2(acc[i + 6], acc[i + 7]);
-          *reinterpret_cast<uint4*>(g.h_out + grow * g.N + ocol + i) = vh;
-        }
-      }
-      // the 1x128 block of h spans both column halves: exchange the partial maxima
-      float* x = sm.xch() + (unit & 1u) * 256;
-      x[half * 128 + row_in_tile] = amax;
-      __syncwarp();
-      if (lane == 0) mbar_arrive(sm.xbar(unit & 1u));
-      if (!mbar_wait(sm.xbar(unit & 1u), (unit >> 1) & 1u, sm.abort_flag(), g.status,
-                     ST_TIMEOUT_AUX))
+      // Round gate/up to bf16 (the Linear output dtype) and hand the tile to the SwiGLU warps:
+      // row r = 512 bytes = 32 chunks of 16 B (gate chunks 0..15, up chunks 16..31), chunk j
+      // stored at (j ^ (r & 7)) so that rows 8 apart never collide on a bank.
+      if (!mbar_wait(sm.hempty(), (unit & 1u) ^ 1u, sm.abort_flag(), g.status, ST_TIMEOUT_AUX))
         return;
-      amax = fmaxf(x[row_in_tile], x[128 + row_in_tile]);
-      const float s = fmaxf(amax, 1e-4f) * (1.0f / 448.0f);
-      uint8_t* hp = g.h_codes + grow * g.h_ld + ocol;
+      uint8_t* hrow = sm.hand() + row_in_tile * 512;
+      const int sw = row_in_tile & 7;
 #pragma unroll
-      for (int i = 0; i < 64; i += 16) {
-        uint4 vc;
-        vc.x = e4m3x4(acc[i], acc[i + 1], acc[i + 2], acc[i + 3], s);
-        vc.y = e4m3x4(acc[i + 4], acc[i + 5], acc[i + 6], acc[i + 7], s);
-        vc.z = e4m3x4(acc[i + 8], acc[i + 9], acc[i + 10], acc[i + 11], s);
-        vc.w = e4m3x4(acc[i + 12], acc[i + 13], acc[i + 14], acc[i + 15], s);
-        *reinterpret_cast<uint4*>(hp + i) = vc;
+      for (int i = 0; i < 16; ++i) {
+        const int j = (i >> 3) * 16 + half * 8 + (i & 7);
+        const float* a8 = acc + i * 8;
+        uint4 v;
+        v.x = pack_bf16x2(a8[0], a8[1]); v.y = pack_bf16x2(a8[2], a8[3]);
+        v.z = pack_bf16x2(a8[4], a8[5]); v.w = pack_bf16x2(a8[6], a8[7]);
+        *reinterpret_cast<uint4*>(hrow + ((j ^ sw) << 4)) = v;
       }
-      if (half == 0) g.h_scale[nt * g.h_scale_nb_stride + grow] = s;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(sm.hfull());
     } else {
       const long long ocol = static_cast<long long>(nt) * kBN + half * 128;
       __nv_bfloat16* cp = g.c_out + grow * g.c_ld + ocol;
@@ -364,27 +366,104 @@ __device__ __forceinline__ void role_epilogue(const GemmArgs& g, const Smem& sm,
   }
 }
 
+// ------------------------------------------------------------------------------ SwiGLU warps
+// 4 warps, thread = row.  Reads the bf16 gate|up tile, h = bf16(w * silu(min(g, L)) *
+// clamp(u, +-L)), 1x128 quantisation of the row's 128 h values (act_quant arithmetic), stores.
+template <class SM>
+__device__ __forceinline__ void role_swiglu(const GemmArgs& g, const SM& sm, int fw, int lane) {
+  const int row_in_tile = fw * 32 + lane;
+  const int sw = row_in_tile & 7;
+  const uint8_t* hrow = sm.hand() + row_in_tile * 512;
+  uint32_t unit = 0;
+  NV41_FOR_EACH_UNIT(g, mt, nt, e) {
+    const long long grow = static_cast<long long>(mt) * kBM + row_in_tile;
+    const float wr = g.row_weight[grow];
+    const float L = g.limit;
+    const long long ocol = static_cast<long long>(nt) * 128;
+    if (!mbar_wait(sm.hfull(), unit & 1u, sm.abort_flag(), g.status, ST_TIMEOUT_AUX)) return;
+    uint32_t hp[64];
+    __nv_bfloat162 amax2 = __floats2bfloat162_rn(0.f, 0.f);
+#pragma unroll
+    for (int jj = 0; jj < 16; ++jj) {
+      const uint4 g8 = *reinterpret_cast<const uint4*>(hrow + ((jj ^ sw) << 4));
+      const uint4 u8 = *reinterpret_cast<const uint4*>(hrow + (((16 + jj) ^ sw) << 4));
+      if (g.gate_out) {
+        *reinterpret_cast<uint4*>(g.gate_out + grow * g.N + ocol + jj * 8) = g8;
+        *reinterpret_cast<uint4*>(g.up_out + grow * g.N + ocol + jj * 8) = u8;
+      }
+      const uint32_t gw_[4] = {g8.x, g8.y, g8.z, g8.w};
+      const uint32_t uw_[4] = {u8.x, u8.y, u8.z, u8.w};
+#pragma unroll
+      for (int p = 0; p < 4; ++p) {
+        float h2[2];
+#pragma unroll
+        for (int t = 0; t < 2; ++t) {
+          float gt = t ? bf16_hi(gw_[p]) : bf16_lo(gw_[p]);
+          float up = t ? bf16_hi(uw_[p]) : bf16_lo(uw_[p]);
+          if (L > 0.f) {
+            up = fminf(fmaxf(up, -L), L);
+            gt = fminf(gt, L);
+          }
+          const float hg = 0.5f * gt;                       // silu(g) = g/2 * (1 + tanh(g/2))
+          const float sl = fmaf(hg, tanh_approx(hg), hg);
+          h2[t] = (sl * up) * wr;
+        }
+        const uint32_t packed = pack_bf16x2(h2[0], h2[1]);
+        hp[jj * 4 + p] = packed;
+        amax2 = __hmax2(amax2, __habs2(*reinterpret_cast<const __nv_bfloat162*>(&packed)));
+      }
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(sm.hempty());   // the hand-off tile may be overwritten
+    if (g.h_out) {
+#pragma unroll
+      for (int jj = 0; jj < 16; ++jj)
+        *reinterpret_cast<uint4*>(g.h_out + grow * g.N + ocol + jj * 8) =
+            make_uint4(hp[jj * 4], hp[jj * 4 + 1], hp[jj * 4 + 2], hp[jj * 4 + 3]);
+    }
+    const float amax = fmaxf(__low2float(amax2), __high2float(amax2));
+    const float s = fmaxf(amax, 1e-4f) * (1.0f / 448.0f);
+    const float r = __frcp_rn(s);
+    uint8_t* hc = g.h_codes + grow * g.h_ld + ocol;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      uint32_t wds[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const uint32_t p0 = hp[i * 8 + j * 2], p1 = hp[i * 8 + j * 2 + 1];
+        wds[j] = e4m3x4(bf16_lo(p0), bf16_hi(p0), bf16_lo(p1), bf16_hi(p1), s, r);
+      }
+      *reinterpret_cast<uint4*>(hc + i * 16) = make_uint4(wds[0], wds[1], wds[2], wds[3]);
+    }
+    g.h_scale[nt * g.h_scale_nb_stride + grow] = s;
+    ++unit;
+  }
+}
+
 // ------------------------------------------------------------------------------ kernel
 template <int MODE_A, int EPI>
 __global__ void __launch_bounds__(kThreads, 1)
 grouped_gemm_fp8_kernel(const __grid_constant__ GemmArgs g) {
+  constexpr int NS = (EPI == EPI_SWIGLU) ? 3 : 4;
+  using SM = Smem<NS, EPI == EPI_SWIGLU>;
   extern __shared__ uint8_t smem_raw[];
-  Smem sm;
+  SM sm;
   sm.base = reinterpret_cast<uint8_t*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
-    const uint32_t full_count = (MODE_A == A_TMA) ? 1u : 5u;   // TMA thread (+ 4 producer warps)
-    for (int s = 0; s < kStages; ++s) {
+    const uint32_t full_count = (MODE_A == A_TMA) ? 1u : 3u;   // TMA thread (+ 2 gather warps)
+    for (int s = 0; s < NS; ++s) {
       mbar_init(sm.full(s), full_count);
       mbar_init(sm.empty(s), 1u);
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(sm.tfull(b), 1u);
-      mbar_init(sm.tempty(b), 8u);      // one arrival per epilogue warp
-      mbar_init(sm.xbar(b), 8u);
+      mbar_init(sm.tempty(b), 8u);      // one arrival per promotion warp
     }
+    mbar_init(sm.hfull(), 8u);
+    mbar_init(sm.hempty(), 4u);
     *sm.abort_flag() = 0u;
     fence_mbar_init();
     tma_prefetch_desc(&g.tmap_b);
@@ -401,18 +480,20 @@ grouped_gemm_fp8_kernel(const __grid_constant__ GemmArgs g) {
 
   const int wg = warp >> 2;
   if (wg == 0) {
-    setmaxnreg_dec<56>();
+    setmaxnreg_dec<64>();
     if (warp == 0) {
-      if (lane == 0) role_tma<MODE_A, EPI>(g, sm);
+      if (lane == 0) role_tma<MODE_A, EPI>(g, sm, NS);
     } else if (warp == 1) {
-      if (lane == 0) role_mma(g, sm, tmem_base);
+      if (lane == 0) role_mma(g, sm, tmem_base, NS);
+    } else if (MODE_A != A_TMA) {
+      role_gather<MODE_A>(g, sm, warp - 2, lane, NS);
     }
   } else if (wg == 1) {
-    setmaxnreg_dec<104>();
-    if (MODE_A != A_TMA) role_gather<MODE_A>(g, sm, warp - 4, lane);
+    setmaxnreg_dec<112>();
+    if (EPI == EPI_SWIGLU) role_swiglu(g, sm, warp - 4, lane);
   } else {
-    setmaxnreg_inc<176>();
-    role_epilogue<MODE_A, EPI>(g, sm, tmem_base, warp - 8, lane);
+    setmaxnreg_inc<168>();
+    role_promote<MODE_A, EPI>(g, sm, tmem_base, warp - 8, lane);
   }
 
   tc_fence_before_sync();
@@ -478,6 +559,7 @@ static int sm_count() {
 template <int MODE_A, int EPI>
 static int launch(const GemmArgs& a, cudaStream_t st) {
   static bool configured = false;
+  constexpr int kSmemBytes = Smem<(EPI == EPI_SWIGLU) ? 3 : 4, EPI == EPI_SWIGLU>::kBytes;
   auto kern = grouped_gemm_fp8_kernel<MODE_A, EPI>;
   if (!configured) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) !=

@@ -244,9 +244,9 @@ extern "C" int nv41_quant_fp8_1x128(const void* x_bf16, long long ld_x, const in
                                     long long rows, int K, void* codes, float* scales,
                                     long long scale_stride_row, long long scale_stride_kb,
                                     void* stream) {
+  if (rows == 0) return NV41_OK;
   if (!x_bf16 || !codes || !scales || rows < 0 || K <= 0 || (K % 8) != 0 || ld_x < K)
     return NV41_ERR_INVALID;
-  if (rows == 0) return NV41_OK;
   const int Kpad = (K + 127) / 128 * 128;
   const long long items = rows * (Kpad / 128);
   long long blocks = (items * 16 + 255) / 256;

@@ -1,4 +1,4 @@
-"""Seeded synthetic workloads shared by the GPU tests, smoke() and bench.py."""
+"""Seeded synthetic workloads (BASELINE configs) shared by the tests, smoke() and bench.py."""
 from __future__ import annotations
 
 import torch
@@ -28,3 +28,13 @@ def make_case(T, E, k, D, I, seed=0, zipf=True, outliers=True, empty_expert=None
     w = w / w.sum(-1, keepdim=True) * 1.5
     out = dict(x=x, w1=w1, w3=w3, w2=w2, indices=idx, weights=w.float())
     return {n: t.to(device) for n, t in out.items()}
+
+
+# BASELINE.json configs that are standalone expert-path workloads
+C2 = dict(T=16384, E=64, k=6, D=1024, I=1024, seed=1, zipf=True, outliers=True)
+C5 = dict(T=131072, E=256, k=8, D=2048, I=1024, seed=2, zipf=False, outliers=False)
+
+
+def fwd_flops(T: int, k: int, D: int, I: int) -> float:
+    """Algorithmic FLOPs of the routed experts' forward: 2*R*D*2I + 2*R*I*D = 6*R*D*I."""
+    return 6.0 * T * k * D * I

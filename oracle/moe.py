@@ -67,18 +67,31 @@ def quantize_weights_fp8(w1, w3, w2):
     return (c13, s13), (c2, s2)
 
 
-def moe_fp8(x, w1, w3, w2, weights, indices, limit, shared=None, return_parts=False):
+def prepare_weights_fp8(w1, w3, w2):
+    """Quantise the expert weights 128x128 and return them dequantised to fp32
+    (w13d [E, 2I, D], w2d [E, D, I]) together with the codes/scales."""
+    E, I, D = w1.shape
+    (c13, s13), (c2, s2) = quantize_weights_fp8(w1, w3, w2)
+    w13d = Q.fp8_dequant_128x128(c13, s13)[:, :, :D].contiguous()
+    w2d = Q.fp8_dequant_128x128(c2, s2)[:, :, :I].contiguous()
+    return dict(w13d=w13d, w2d=w2d, w13=(c13, s13), w2=(c2, s2), E=E, I=I, D=D)
+
+
+def moe_fp8(x, w1, w3, w2, weights, indices, limit, shared=None, return_parts=False,
+            prepared=None):
     """Dequantise-then-fp32-matmul oracle of the FP8 expert path (forward).
 
     x -> act_quant 1x128 (per token row) -> dequant -> @ dequant(W13)^T in fp32 -> bf16
     -> fp32 SwiGLU (+clamp, x routing weight) -> bf16 h -> act_quant 1x128 -> dequant
     -> @ dequant(W2)^T fp32 -> bf16 -> fp32 sum over slots (+ shared) -> bf16.
-    Scale semantics: ref/kernel.py:207-274 (fp8_gemm: C += (A_q B_q^T)_kblock * sa * sb)."""
+    Scale semantics: ref/kernel.py:207-274 (fp8_gemm: C += (A_q B_q^T)_kblock * sa * sb).
+    ``prepared`` = prepare_weights_fp8(...) skips the weight quantisation (w1/w3/w2 unused)."""
     T, k = indices.shape
-    E, I, D = w1.shape
-    (c13, s13), (c2, s2) = quantize_weights_fp8(w1, w3, w2)
-    w13d = Q.fp8_dequant_128x128(c13, s13)[:, :, :D]          # [E, 2I, D]
-    w2d = Q.fp8_dequant_128x128(c2, s2)[:, :, :I]             # [E, D, I]
+    if prepared is None:
+        prepared = prepare_weights_fp8(w1, w3, w2)
+    E, I, D = prepared["E"], prepared["I"], prepared["D"]
+    w13d, w2d = prepared["w13d"], prepared["w2d"]
+    (c13, s13), (c2, s2) = prepared["w13"], prepared["w2"]
     xc, xsc = Q.fp8_quant_1x128(x)
     xd = Q.fp8_dequant_1x128(xc, xsc)[:, :D]                  # [T, D] fp32
     order, tok, counts = sort_tokens(indices, E)
@@ -99,7 +112,8 @@ def moe_fp8(x, w1, w3, w2, weights, indices, limit, shared=None, return_parts=Fa
             hc, hs = Q.fp8_quant_1x128(h)
             hd = Q.fp8_dequant_1x128(hc, hs)[:, :I]
             outs[pos:pos + c] = (hd @ w2d[e].t()).to(torch.bfloat16)
-            gate_all[pos:pos + c], up_all[pos:pos + c], h_all[pos:pos + c] = gate, up, h
+            if return_parts:
+                gate_all[pos:pos + c], up_all[pos:pos + c], h_all[pos:pos + c] = gate, up, h
         pos += c
     flat = torch.empty(R, D, dtype=torch.float32)
     flat.index_copy_(0, order, outs.float())

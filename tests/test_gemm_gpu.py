@@ -8,7 +8,7 @@ scales are compared bit-for-bit.
 import pytest
 import torch
 
-from moe_cases import make_case
+from nanov41_b200.workloads import make_case
 from oracle import moe as OM
 from oracle import quant as OQ
 
