@@ -85,6 +85,25 @@ int nv41_moe_layout_build(const void* expert_idx, int idx_is_i64, const float* w
                           int* row_of_flat, int* flat_of_row, int* row_token, float* row_weight,
                           int* tile_expert, int* meta, int* status, void* stream);
 
+/* No counterpart in the reference.  Same result as nv41_moe_layout_build, for callers that
+ * cannot obtain device memory where they need a layout (a hook that must not touch the
+ * allocator, a plugin given only fixed input/output buffers, a process whose memory pool
+ * belongs to another component): there is no workspace argument, the histogram scratch is a
+ * fixed 4 MiB device array inside the library (resident on every GPU that loads it), and the
+ * call performs no allocation of any kind.  Limit: ceil(R/256) * E <= 1,048,576 entries
+ * (nv41_moe_layout_static_capacity()), otherwise NV41_ERR_UNSUPPORTED.  The first call on each
+ * device looks up the array's device address (with that device current), so make that first
+ * call outside any stream capture.  All calls on a device share the one array: calls whose
+ * kernels can overlap on the GPU (different streams) race and must be serialised by the caller;
+ * stale contents from an earlier call never matter because every entry is rewritten first. */
+long long nv41_moe_layout_static_capacity(void);
+int nv41_moe_layout_build_static(const void* expert_idx, int idx_is_i64,
+                                 const float* weights_flat, long long R, int E, int k,
+                                 long long P_max, int* counts, int* cum_excl, int* pad_off,
+                                 int* order, int* pad_pos, int* row_of_flat, int* flat_of_row,
+                                 int* row_token, float* row_weight, int* tile_expert, int* meta,
+                                 int* status, void* stream);
+
 /* Un-permute + top-k sum (+ shared expert) with fp32 accumulation and one bf16 rounding;
  * nanov41/fast_moe.py:311-338,467-474 (_scatter_topk + shared add),
  * nanov41/triton_grouped_moe.py:1193-1207 (_moe_tail_fwd_kernel).

@@ -226,25 +226,23 @@ extern "C" long long nv41_moe_layout_workspace_bytes(long long R, int E) {
   return (n_runs > 0 ? n_runs : 1) * E * static_cast<long long>(sizeof(int));
 }
 
-extern "C" int nv41_moe_layout_build(const void* expert_idx, int idx_is_i64,
-                                     const float* weights_flat, long long R, int E, int k,
-                                     long long P_max, void* workspace, int* counts, int* cum_excl,
-                                     int* pad_off, int* order, int* pad_pos, int* row_of_flat,
-                                     int* flat_of_row, int* row_token, float* row_weight,
-                                     int* tile_expert, int* meta, int* status, void* stream) {
-  if (!expert_idx || R < 0 || E <= 0 || E > 2048 || k <= 0 || !workspace || !counts ||
-      !cum_excl || !pad_off || !order || !pad_pos || !row_of_flat || !flat_of_row ||
-      !row_token || !tile_expert || !meta || !status)
+static int layout_build_impl(const void* expert_idx, int idx_is_i64, const float* weights_flat,
+                             long long R, int E, int k, long long P_max, int* hist, int* counts,
+                             int* cum_excl, int* pad_off, int* order, int* pad_pos,
+                             int* row_of_flat, int* flat_of_row, int* row_token,
+                             float* row_weight, int* tile_expert, int* meta, int* status,
+                             cudaStream_t st) {
+  if (!expert_idx || R < 0 || E <= 0 || E > 2048 || k <= 0 || !hist || !counts || !cum_excl ||
+      !pad_off || !order || !pad_pos || !row_of_flat || !flat_of_row || !row_token ||
+      !tile_expert || !meta || !status)
     return NV41_ERR_INVALID;
-  if (P_max % 128 != 0 || P_max < R + 0) return NV41_ERR_INVALID;
+  if (P_max % 128 != 0 || P_max < R) return NV41_ERR_INVALID;
   if (row_weight && !weights_flat) return NV41_ERR_INVALID;
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int n_runs = static_cast<int>((R + kRun - 1) / kRun);
   const int n_tiles_max = static_cast<int>(P_max / 128);
   const int ctas = n_runs > 0 ? (n_runs + kWarpsPerCta - 1) / kWarpsPerCta : 1;
   const size_t sh_warp = static_cast<size_t>(kWarpsPerCta) * E * sizeof(int);
   if (sh_warp > 48 * 1024) return NV41_ERR_UNSUPPORTED;
-  int* hist = static_cast<int*>(workspace);
   layout_hist_kernel<<<ctas, kWarpsPerCta * 32, sh_warp, st>>>(
       expert_idx, idx_is_i64, R, E, n_runs, hist, P_max, flat_of_row, row_token, row_weight,
       status);
@@ -256,6 +254,61 @@ extern "C" int nv41_moe_layout_build(const void* expert_idx, int idx_is_i64,
         pad_pos, row_of_flat, flat_of_row, row_token, row_weight);
   }
   return launch_status();
+}
+
+extern "C" int nv41_moe_layout_build(const void* expert_idx, int idx_is_i64,
+                                     const float* weights_flat, long long R, int E, int k,
+                                     long long P_max, void* workspace, int* counts, int* cum_excl,
+                                     int* pad_off, int* order, int* pad_pos, int* row_of_flat,
+                                     int* flat_of_row, int* row_token, float* row_weight,
+                                     int* tile_expert, int* meta, int* status, void* stream) {
+  return layout_build_impl(expert_idx, idx_is_i64, weights_flat, R, E, k, P_max,
+                           static_cast<int*>(workspace), counts, cum_excl, pad_off, order,
+                           pad_pos, row_of_flat, flat_of_row, row_token, row_weight, tile_expert,
+                           meta, status, static_cast<cudaStream_t>(stream));
+}
+
+// ---- layout build for callers that must not allocate -----------------------------------------
+// The per-run histogram scratch of the layout build normally comes from the caller.  Some
+// callers have no way to get device memory at the point where they need a layout: code running
+// inside a framework hook that is forbidden to touch the allocator, a plugin that is handed
+// fixed input/output buffers and nothing else, or a process whose memory pool is owned by
+// another component.  For them the scratch lives in this fixed device array, which every GPU
+// that loads the library carries until the process exits (kStaticScratchInts * 4 bytes = 4 MiB).
+constexpr long long kStaticScratchInts = 1LL << 20;   // (R / 256 runs) * E entries at most
+static __device__ __align__(256) int g_layout_scratch[kStaticScratchInts];
+
+constexpr int kMaxDevices = 64;
+static int* g_layout_scratch_ptr[kMaxDevices] = {nullptr};
+
+extern "C" long long nv41_moe_layout_static_capacity(void) { return kStaticScratchInts; }
+
+extern "C" int nv41_moe_layout_build_static(const void* expert_idx, int idx_is_i64,
+                                            const float* weights_flat, long long R, int E, int k,
+                                            long long P_max, int* counts, int* cum_excl,
+                                            int* pad_off, int* order, int* pad_pos,
+                                            int* row_of_flat, int* flat_of_row, int* row_token,
+                                            float* row_weight, int* tile_expert, int* meta,
+                                            int* status, void* stream) {
+  if (R < 0 || E <= 0) return NV41_ERR_INVALID;
+  const long long n_runs = (R + kRun - 1) / kRun;
+  if (n_runs * E > kStaticScratchInts) return NV41_ERR_UNSUPPORTED;   // beyond the fixed scratch
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return NV41_ERR_CUDA;
+  if (!g_layout_scratch_ptr[dev]) {
+    // The array's name is only a host-side handle; the device address must be looked up, once
+    // per device, while that device is current.
+    int* p = nullptr;
+    if (cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_layout_scratch) != cudaSuccess || !p)
+      return NV41_ERR_CUDA;
+    g_layout_scratch_ptr[dev] = p;
+  }
+  // Nothing in the scratch has to start at zero: the histogram pass overwrites every entry the
+  // later passes read (n_runs * E of them), so contents left by an earlier call are harmless.
+  return layout_build_impl(expert_idx, idx_is_i64, weights_flat, R, E, k, P_max,
+                           g_layout_scratch_ptr[dev], counts, cum_excl, pad_off, order, pad_pos,
+                           row_of_flat, flat_of_row, row_token, row_weight, tile_expert, meta,
+                           status, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int nv41_moe_combine(const void* y_rows_bf16, const int* row_of_flat,

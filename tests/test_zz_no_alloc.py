@@ -1,0 +1,64 @@
+"""GPU: the layout build that allocates nothing (its scratch is a fixed device array inside the
+library, for callers that cannot obtain device memory) must give exactly the tables of the
+ordinary entry point -- on two calls in a row, so leftovers of the first call in the shared
+scratch cannot leak into the second.  Runs last (file name) and alone equally well."""
+import ctypes as C
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _call_static(lib, idx, weights, E, k, P):
+    dev = idx.device
+    R = idx.numel()
+    i32 = dict(dtype=torch.int32, device=dev)
+    out = dict(counts=torch.empty(E, **i32), cum_excl=torch.empty(E + 1, **i32),
+               pad_off=torch.empty(E + 1, **i32), order=torch.empty(R, **i32),
+               pad_pos=torch.empty(R, **i32), row_of_flat=torch.empty(R, **i32),
+               flat_of_row=torch.empty(P, **i32), row_token=torch.empty(P, **i32),
+               row_weight=torch.empty(P, dtype=torch.float32, device=dev),
+               tile_expert=torch.empty(P // 128, **i32), meta=torch.empty(4, **i32),
+               status=torch.zeros(1, **i32))
+    p = lambda t: C.c_void_p(t.data_ptr())
+    before = torch.cuda.memory_allocated(dev)
+    rc = lib.nv41_moe_layout_build_static(
+        p(idx), int(idx.dtype == torch.int64), p(weights), R, E, k, P, p(out["counts"]),
+        p(out["cum_excl"]), p(out["pad_off"]), p(out["order"]), p(out["pad_pos"]),
+        p(out["row_of_flat"]), p(out["flat_of_row"]), p(out["row_token"]), p(out["row_weight"]),
+        p(out["tile_expert"]), p(out["meta"]), p(out["status"]),
+        C.c_void_p(torch.cuda.current_stream().cuda_stream))
+    assert torch.cuda.memory_allocated(dev) == before
+    return rc, out
+
+
+def test_static_layout_matches_regular_entry_point_twice():
+    from nanov41_b200 import _lib, ops
+    lib = _lib.load()
+    gen = torch.Generator().manual_seed(9)
+    for T, E, k in ((5000, 64, 6), (777, 16, 2)):        # second call: smaller, different E
+        p = 1.0 / torch.arange(1, E + 1).float()
+        idx = torch.multinomial(p.expand(T, E), k, replacement=False, generator=gen).cuda()
+        w = torch.rand(T, k, generator=gen).cuda()
+        ref = ops.build_layout(idx.reshape(-1), E, k, w.reshape(-1))
+        rc, got = _call_static(lib, idx.reshape(-1).contiguous(), w.reshape(-1).contiguous(), E, k,
+                               ref.P_max)
+        assert rc == 0
+        torch.cuda.synchronize()
+        for name, t in got.items():
+            assert torch.equal(t, getattr(ref, name)), name
+
+
+def test_static_layout_rejects_sizes_beyond_its_scratch():
+    from nanov41_b200 import _lib
+    lib = _lib.load()
+    cap = lib.nv41_moe_layout_static_capacity()
+    E = 2048
+    R = (cap // E + 1) * 256                      # one run too many for the fixed array
+    idx = torch.zeros(8, dtype=torch.int32, device="cuda")
+    rc = lib.nv41_moe_layout_build_static(
+        C.c_void_p(idx.data_ptr()), 0, None, R, E, 1, ((R + E * 128) // 128) * 128,
+        *([C.c_void_p(idx.data_ptr())] * 8), None, C.c_void_p(idx.data_ptr()),
+        C.c_void_p(idx.data_ptr()), C.c_void_p(idx.data_ptr()), None)
+    assert rc == _lib.ERR_UNSUPPORTED
