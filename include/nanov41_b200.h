@@ -107,9 +107,10 @@ int nv41_moe_layout_build_static(const void* expert_idx, int idx_is_i64,
 /* Un-permute + top-k sum (+ shared expert) with fp32 accumulation and one bf16 rounding;
  * nanov41/fast_moe.py:311-338,467-474 (_scatter_topk + shared add),
  * nanov41/triton_grouped_moe.py:1193-1207 (_moe_tail_fwd_kernel).
- * y_rows: bf16 [P_max, D]; shared: bf16 [T, D] or NULL; out: bf16 [T, D]; D % 8 == 0. */
+ * y_rows: bf16 [P_max, D]; shared: bf16 [T, D] or NULL; out: [T, D] bf16, or fp32 (the
+ * unrounded sum, as _scatter_topk returns) when out_is_fp32 != 0; D % 8 == 0. */
 int nv41_moe_combine(const void* y_rows_bf16, const int* row_of_flat, const void* shared_bf16,
-                     void* out_bf16, long long T, int k, int D, void* stream);
+                     void* out, int out_is_fp32, long long T, int k, int D, void* stream);
 
 /* ---- grouped FP8 GEMMs (tcgen05 / TMEM) --------------------------------------------------- */
 
@@ -144,6 +145,31 @@ int nv41_moe_gemm_fp8(int a_mode, const void* a_src, long long a_ld, const float
                       int E, int N, int K, const int* tile_expert, const int* row_token,
                       long long P_max, void* c_out, long long c_ld, unsigned* status,
                       void* stream);
+
+/* ---- backward ------------------------------------------------------------------------------ */
+
+/* dst[p] = src[rows[p]] (a zero row where rows[p] < 0); bf16, cols % 8 == 0.  Materialises the
+ * expert-major copies of x and dY (nanov41/triton_grouped_moe.py:1507-1509 x[layout.tok];
+ * :1210-1218 _moe_tail_bwd_kernel). */
+int nv41_gather_rows_bf16(const void* src, long long src_ld, const int* rows, long long n_rows,
+                          int cols, void* dst, void* stream);
+
+/* SwiGLU backward + routing-weight gradient + 1x128 quantisation of [dgate | dup];
+ * nanov41/triton_grouped_moe.py:759-792 (_swiglu_bwd_kernel, strict clamp masks) and :1243-1262
+ * (_moe_dws_kernel).  dact, gate, up: bf16 [P_max, I]; meta from nv41_moe_layout_build.
+ * Outputs: dgate, dup bf16 [P_max, I]; dgu_codes e4m3 [P_max, 2I]; dgu_scales fp32
+ * [2I/128][P_max]; dws fp32 [P_max].  I % 128 == 0. */
+int nv41_swiglu_bwd_quant(const void* dact, const void* gate, const void* up,
+                          const float* row_weight, const int* meta, int I, long long P_max,
+                          float swiglu_limit, void* dgate, void* dup, void* dgu_codes,
+                          float* dgu_scales, float* dws, void* stream);
+
+/* Grouped weight gradient out[e] = A[rows_e]^T @ B[rows_e] (bf16 in, fp32 accumulate in TMEM,
+ * bf16 out); nanov41/triton_grouped_moe.py:277-296 (_dw_kernel), :795-862 (_dw13_kernel).
+ * a_rows: bf16 [P_max, M]; b_rows: bf16 [P_max, N] (padding rows zero); pad_off: int32 [E+1];
+ * out: bf16 [E, M, N].  M % 8 == 0, N % 8 == 0. */
+int nv41_moe_wgrad_bf16(const void* a_rows, const void* b_rows, const int* pad_off, int E, int M,
+                        int N, long long P_max, void* out, unsigned* status, void* stream);
 
 #ifdef __cplusplus
 }

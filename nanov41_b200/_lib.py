@@ -29,11 +29,14 @@ SIGNATURES = {
     "nv41_moe_layout_static_capacity": (_ll, []),
     "nv41_moe_layout_build_static": (_i, [_p, _i, _p, _ll, _i, _i, _ll, _p, _p, _p, _p, _p, _p,
                                           _p, _p, _p, _p, _p, _p, _p]),
-    "nv41_moe_combine": (_i, [_p, _p, _p, _p, _ll, _i, _i, _p]),
+    "nv41_moe_combine": (_i, [_p, _p, _p, _p, _i, _ll, _i, _i, _p]),
     "nv41_moe_gemm1_fp8": (_i, [_i, _p, _ll, _i, _p, _ll, _ll, _p, _p, _i, _i, _i, _p, _p, _p,
                                 _ll, _f, _p, _p, _p, _p, _p, _p, _p]),
     "nv41_moe_gemm_fp8": (_i, [_i, _p, _ll, _p, _ll, _ll, _p, _p, _ll, _ll, _ll, _i, _i, _i,
                                _p, _p, _ll, _p, _ll, _p, _p]),
+    "nv41_gather_rows_bf16": (_i, [_p, _ll, _p, _ll, _i, _p, _p]),
+    "nv41_swiglu_bwd_quant": (_i, [_p, _p, _p, _p, _p, _i, _ll, _f, _p, _p, _p, _p, _p, _p]),
+    "nv41_moe_wgrad_bf16": (_i, [_p, _p, _p, _i, _i, _i, _ll, _p, _p, _p]),
 }
 
 _lib = None

@@ -1,0 +1,180 @@
+// HBM-bound helpers of the expert-path backward.
+//
+//  * gather_rows: dst[p] = src[row_token[p]] (zero row for padding) -- materialises the
+//    expert-major copies of x and dY that the weight-gradient GEMM reads by TMA
+//    (reference: x_sorted = x[layout.tok], nanov41/triton_grouped_moe.py:1507-1509, and
+//    _moe_tail_bwd_kernel :1210-1218 for dY).
+//  * swiglu_bwd_quant: from dact = dY @ W2 (bf16) and the saved gate/up, the SwiGLU backward of
+//    nanov41/triton_grouped_moe.py:759-792 (_swiglu_bwd_kernel; strict-inequality clamp masks on
+//    the clamped values, :789-790) and the routing-weight gradient of :1243-1262 (_moe_dws_kernel):
+//        dgate = [gc < L]   * dact * w * uc * sig(gc) (1 + gc (1 - sig(gc)))
+//        dup   = [|uc| < L] * dact * w * gc * sig(gc)
+//        dws   = sum_i dact_i * gc_i sig(gc_i) * uc_i
+//    dgate/dup are rounded to bf16 (kept for the weight-gradient GEMM) and quantised 1x128 to
+//    e4m3 as the A operand [dgate | dup] of the dX GEMM (the in-kernel activation quantisation of
+//    _aggemm_tb_fp8_kernel, :1071-1093, done once instead of once per N tile).
+#include <cuda_bf16.h>
+#include <cuda_fp8.h>
+#include <cstdint>
+
+#include "../../include/nanov41_b200.h"
+#include "util.cuh"
+
+namespace nv41 {
+
+__global__ void __launch_bounds__(256)
+gather_rows_kernel(const uint4* __restrict__ src, long long src_ld16, const int* __restrict__ rows,
+                   uint4* __restrict__ dst, long long n_rows, int chunks) {
+  const long long total = n_rows * chunks;
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += stride) {
+    const long long r = i / chunks;
+    const int c = static_cast<int>(i - r * chunks);
+    const int s = rows[r];
+    dst[i] = s >= 0 ? __ldg(src + s * src_ld16 + c) : make_uint4(0u, 0u, 0u, 0u);
+  }
+}
+
+__device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    f[2 * i] = __uint_as_float(w[i] << 16);
+    f[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+  }
+}
+__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
+  uint32_t o[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const __nv_bfloat162 b = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+    o[i] = *reinterpret_cast<const uint32_t*>(&b);
+  }
+  return make_uint4(o[0], o[1], o[2], o[3]);
+}
+__device__ __forceinline__ uint2 quant8(const float (&f)[8], float s) {
+  uint32_t w[2];
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    float q[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) q[i] = fminf(fmaxf(__fdiv_rn(f[4 * h + i], s), -448.f), 448.f);
+    const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(q[0], q[1]), __NV_SATFINITE, __NV_E4M3);
+    const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(q[2], q[3]), __NV_SATFINITE, __NV_E4M3);
+    w[h] = lo | (hi << 16);
+  }
+  return make_uint2(w[0], w[1]);
+}
+
+// One warp per padded row; a half-warp (16 lanes x 8 columns) covers one 1x128 block.
+__global__ void __launch_bounds__(256)
+swiglu_bwd_quant_kernel(const __nv_bfloat16* __restrict__ dact, const __nv_bfloat16* __restrict__ gate,
+                        const __nv_bfloat16* __restrict__ up, const float* __restrict__ row_weight,
+                        const int* __restrict__ meta, int I, long long P_max, float L,
+                        __nv_bfloat16* __restrict__ dgate, __nv_bfloat16* __restrict__ dup,
+                        uint8_t* __restrict__ codes, float* __restrict__ scales,
+                        float* __restrict__ dws) {
+  const int lane = threadIdx.x & 31;
+  const long long warp0 = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const long long nwarps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
+  const long long used = meta[1];                 // padded rows in use
+  const unsigned hmask = 0xFFFFu << (lane & 16);
+  const int nblk = I / 128;
+  for (long long p = warp0; p < used; p += nwarps) {
+    const float w = row_weight[p];
+    float dws_acc = 0.f;
+    for (int c0 = 0; c0 < I; c0 += 256) {
+      const int col = c0 + lane * 8;
+      const bool in = col < I;
+      float d[8], g[8], u[8], dg[8], du[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) d[i] = g[i] = u[i] = 0.f;
+      if (in) {
+        unpack8(__ldg(reinterpret_cast<const uint4*>(dact + p * I + col)), d);
+        unpack8(__ldg(reinterpret_cast<const uint4*>(gate + p * I + col)), g);
+        unpack8(__ldg(reinterpret_cast<const uint4*>(up + p * I + col)), u);
+      }
+      float am_g = 0.f, am_u = 0.f;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        float gc = g[i], uc = u[i];
+        bool mg = true, mu = true;
+        if (L > 0.f) {
+          gc = fminf(gc, L);
+          uc = fminf(fmaxf(uc, -L), L);
+          mg = gc < L;
+          mu = fabsf(uc) < L;
+        }
+        const float sig = 1.f / (1.f + __expf(-gc));
+        const float silu = gc * sig;
+        const float dsilu = sig * (1.f + gc * (1.f - sig));
+        const float dw = d[i] * w;
+        dws_acc = fmaf(d[i], silu * uc, dws_acc);
+        // round to bf16 first: the quantizer sees the stored bf16 values
+        dg[i] = __bfloat162float(__float2bfloat16_rn(mg ? dw * uc * dsilu : 0.f));
+        du[i] = __bfloat162float(__float2bfloat16_rn(mu ? dw * silu : 0.f));
+        am_g = fmaxf(am_g, fabsf(dg[i]));
+        am_u = fmaxf(am_u, fabsf(du[i]));
+      }
+#pragma unroll
+      for (int o = 8; o >= 1; o >>= 1) {
+        am_g = fmaxf(am_g, __shfl_xor_sync(hmask, am_g, o));
+        am_u = fmaxf(am_u, __shfl_xor_sync(hmask, am_u, o));
+      }
+      if (in) {
+        const float sg = fmaxf(am_g, 1e-4f) * (1.0f / 448.0f);
+        const float su = fmaxf(am_u, 1e-4f) * (1.0f / 448.0f);
+        *reinterpret_cast<uint4*>(dgate + p * I + col) = pack8(dg);
+        *reinterpret_cast<uint4*>(dup + p * I + col) = pack8(du);
+        *reinterpret_cast<uint2*>(codes + p * 2 * I + col) = quant8(dg, sg);
+        *reinterpret_cast<uint2*>(codes + p * 2 * I + I + col) = quant8(du, su);
+        if ((lane & 15) == 0) {
+          const int kb = col / 128;
+          scales[static_cast<long long>(kb) * P_max + p] = sg;
+          scales[static_cast<long long>(nblk + kb) * P_max + p] = su;
+        }
+      }
+    }
+#pragma unroll
+    for (int o = 16; o >= 1; o >>= 1) dws_acc += __shfl_xor_sync(0xFFFFFFFFu, dws_acc, o);
+    if (lane == 0) dws[p] = dws_acc;
+  }
+}
+
+}  // namespace nv41
+
+using namespace nv41;
+
+extern "C" int nv41_gather_rows_bf16(const void* src, long long src_ld, const int* rows,
+                                     long long n_rows, int cols, void* dst, void* stream) {
+  if (n_rows == 0) return NV41_OK;
+  if (!src || !rows || !dst || n_rows < 0 || cols <= 0 || (cols % 8) != 0 || (src_ld % 8) != 0)
+    return NV41_ERR_INVALID;
+  long long blocks = (n_rows * (cols / 8) + 255) / 256;
+  if (blocks > 148LL * 32) blocks = 148LL * 32;
+  gather_rows_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint4*>(src), src_ld / 8, rows, static_cast<uint4*>(dst), n_rows,
+      cols / 8);
+  return launch_status();
+}
+
+extern "C" int nv41_swiglu_bwd_quant(const void* dact, const void* gate, const void* up,
+                                     const float* row_weight, const int* meta, int I,
+                                     long long P_max, float swiglu_limit, void* dgate, void* dup,
+                                     void* dgu_codes, float* dgu_scales, float* dws,
+                                     void* stream) {
+  if (!dact || !gate || !up || !row_weight || !meta || !dgate || !dup || !dgu_codes ||
+      !dgu_scales || !dws || I <= 0 || P_max <= 0)
+    return NV41_ERR_INVALID;
+  if ((I % 128) != 0) return NV41_ERR_UNSUPPORTED;
+  long long blocks = (P_max + 7) / 8;
+  if (blocks > 148LL * 16) blocks = 148LL * 16;
+  swiglu_bwd_quant_kernel<<<static_cast<unsigned>(blocks), 256, 0,
+                            static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(dact), static_cast<const __nv_bfloat16*>(gate),
+      static_cast<const __nv_bfloat16*>(up), row_weight, meta, I, P_max, swiglu_limit,
+      static_cast<__nv_bfloat16*>(dgate), static_cast<__nv_bfloat16*>(dup),
+      static_cast<uint8_t*>(dgu_codes), dgu_scales, dws);
+  return launch_status();
+}

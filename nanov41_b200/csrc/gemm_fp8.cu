@@ -32,6 +32,7 @@
 
 #include "../../include/nanov41_b200.h"
 #include "ptx.cuh"
+#include "tmap.cuh"
 #include "util.cuh"
 
 namespace nv41 {
@@ -508,52 +509,9 @@ grouped_gemm_fp8_kernel(const __grid_constant__ GemmArgs g) {
 }
 
 // ------------------------------------------------------------------------------ host side
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
-                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
-                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn encode_tiled_fn() {
-  static EncodeTiledFn fn = nullptr;
-  static bool tried = false;
-  if (!tried) {
-    tried = true;
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult qres;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) ==
-            cudaSuccess &&
-        qres == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<EncodeTiledFn>(p);
-  }
-  return fn;
-}
-
-// 2-D u8 tensor [rows, cols] (cols contiguous), box 128 rows x 128 bytes, 128-byte swizzle.
 static int make_tmap_u8(CUtensorMap* m, const void* base, unsigned long long rows,
                         unsigned long long cols) {
-  EncodeTiledFn fn = encode_tiled_fn();
-  if (!fn) return NV41_ERR_CUDA;
-  if ((reinterpret_cast<uintptr_t>(base) & 15u) || (cols % 16) != 0) return NV41_ERR_INVALID;
-  const cuuint64_t dims[2] = {cols, rows};
-  const cuuint64_t strides[1] = {cols};
-  const cuuint32_t box[2] = {128, 128};
-  const cuuint32_t estr[2] = {1, 1};
-  const CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims,
-                        strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? NV41_OK : NV41_ERR_CUDA;
-}
-
-static int sm_count() {
-  static int n = 0;
-  if (n == 0) {
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess) return 148;
-    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
-      n = 148;
-  }
-  return n;
+  return make_tmap_2d(m, base, rows, cols, 1, 128, 128);
 }
 
 template <int MODE_A, int EPI>

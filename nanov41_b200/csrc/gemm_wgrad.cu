@@ -1,0 +1,261 @@
+// Grouped weight-gradient GEMM for sm_100a: dW[e] = A_e^T @ B_e with the contraction running over
+// the routed rows of expert e (bf16 operands, fp32 accumulation in TMEM, bf16 out).
+//
+// Reference: nanov41/triton_grouped_moe.py:277-296 (_dw_kernel: dW[e,K,N] = A[rows_e,K]^T @
+// dC[rows_e,N]) and :795-862 (_dw13_kernel: dW1, dW3 share the activation tile); the reference's
+// FP8 class keeps these two GEMMs in bf16 (:1439-1441, :1467, :1479), and so does this kernel.
+//
+// Both operands are row-major [P_max, cols] matrices in the padded row space, i.e. the
+// contraction index is the slow dimension of both: they are fed to tcgen05 (kind::f16) as
+// MN-major operands.  A TMA box of 64 columns x 64 rows with the 128-byte swizzle lands in
+// shared memory exactly as eight 8-row x 128-byte swizzle atoms of the MN-major canonical layout.
+//
+// One persistent CTA per SM, 384 threads: warp 0 TMA producer, warp 1 UMMA issuer (+ TMEM
+// allocation), warps 4-11 epilogue.  Output tile 128 x 256; K step 64 rows (4 UMMAs of K = 16);
+// the accumulator stays in TMEM for the whole K loop (two 256-column buffers, so the epilogue of
+// one unit overlaps the mainloop of the next).  Padding rows are zero in every operand, so each
+// expert's K loop simply covers its padded segment [pad_off[e], pad_off[e+1]).
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cstdint>
+#include <cstring>
+
+#include "../../include/nanov41_b200.h"
+#include "ptx.cuh"
+#include "tmap.cuh"
+#include "util.cuh"
+
+namespace nv41 {
+namespace wgrad {
+
+constexpr int kTM = 128, kTN = 256, kKS = 64;     // tile rows / cols, contraction rows per stage
+constexpr int kBox = 64 * kKS * 2;                // one 64-column box: 8 KiB
+constexpr int kABytes = (kTM / 64) * kBox;        // 16 KiB
+constexpr int kBBytes = (kTN / 64) * kBox;        // 32 KiB
+constexpr int kStageBytes = kABytes + kBBytes;
+constexpr int kStages = 4;
+constexpr int kThreads = 384;
+constexpr int kSmemBytes = kStages * kStageBytes + (2 * kStages + 4) * 8 + 16 + 1024;
+
+struct Args {
+  CUtensorMap tmap_a;            // [P_max, M] bf16, box 64 x 64
+  CUtensorMap tmap_b;            // [P_max, N] bf16, box 64 x 64
+  const int* pad_off;            // [E + 1] padded segment offsets (multiples of 128)
+  __nv_bfloat16* out;            // [E, M, N]
+  int E, M, N, tiles_m, tiles_n;
+  uint32_t* status;
+};
+
+struct Smem {
+  uint8_t* base;
+  __device__ uint8_t* a(int s) const { return base + s * kStageBytes; }
+  __device__ uint8_t* b(int s) const { return base + s * kStageBytes + kABytes; }
+  __device__ uint64_t* bars() const { return reinterpret_cast<uint64_t*>(base + kStages * kStageBytes); }
+  __device__ uint64_t* full(int s) const { return bars() + s; }
+  __device__ uint64_t* empty(int s) const { return bars() + kStages + s; }
+  __device__ uint64_t* tfull(int b) const { return bars() + 2 * kStages + b; }
+  __device__ uint64_t* tempty(int b) const { return bars() + 2 * kStages + 2 + b; }
+  __device__ uint32_t* tmem_slot() const { return reinterpret_cast<uint32_t*>(bars() + 2 * kStages + 4); }
+  __device__ volatile uint32_t* abort_flag() const { return tmem_slot() + 1; }
+};
+
+struct Unit {
+  int e, mt, nt, ksteps, row0;
+};
+__device__ __forceinline__ Unit decode(const Args& g, int u) {
+  Unit r;
+  r.e = u % g.E;
+  const int t = u / g.E;
+  r.mt = t / g.tiles_n;
+  r.nt = t - r.mt * g.tiles_n;
+  r.row0 = g.pad_off[r.e];
+  r.ksteps = (g.pad_off[r.e + 1] - r.row0) / kKS;
+  return r;
+}
+
+__global__ void __launch_bounds__(kThreads, 1) wgrad_kernel(const __grid_constant__ Args g) {
+  extern __shared__ uint8_t smem_raw[];
+  Smem sm;
+  sm.base = reinterpret_cast<uint8_t*>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(sm.full(s), 1u);
+      mbar_init(sm.empty(s), 1u);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(sm.tfull(b), 1u);
+      mbar_init(sm.tempty(b), 8u);
+    }
+    *sm.abort_flag() = 0u;
+    fence_mbar_init();
+    tma_prefetch_desc(&g.tmap_a);
+    tma_prefetch_desc(&g.tmap_b);
+  }
+  if (warp == 1) {
+    tmem_alloc(sm.tmem_slot(), 512);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *sm.tmem_slot();
+  const int total = g.E * g.tiles_m * g.tiles_n;
+
+  if (warp == 0 && lane == 0) {
+    // ---------------------------------------------------------------- TMA producer
+    uint32_t it = 0;
+    for (int u = blockIdx.x; u < total; u += gridDim.x) {
+      const Unit un = decode(g, u);
+      for (int ks = 0; ks < un.ksteps; ++ks, ++it) {
+        const int s = it % kStages;
+        const uint32_t ph = (it / kStages) & 1u;
+        if (!mbar_wait(sm.empty(s), ph ^ 1u, sm.abort_flag(), g.status, ST_TIMEOUT_EMPTY)) break;
+        mbar_arrive_expect_tx(sm.full(s), kStageBytes);
+        const int row = un.row0 + ks * kKS;
+#pragma unroll
+        for (int i = 0; i < kTM / 64; ++i)
+          tma_load_2d(sm.a(s) + i * kBox, &g.tmap_a, un.mt * kTM + i * 64, row, sm.full(s));
+#pragma unroll
+        for (int i = 0; i < kTN / 64; ++i)
+          tma_load_2d(sm.b(s) + i * kBox, &g.tmap_b, un.nt * kTN + i * 64, row, sm.full(s));
+      }
+      if (*sm.abort_flag()) break;
+    }
+  } else if (warp == 1 && lane == 0) {
+    // ---------------------------------------------------------------- UMMA issuer
+    constexpr uint32_t idesc = umma_idesc(kTM, kTN, 1, 1, 1, 1);   // bf16 x bf16, both MN-major
+    uint32_t it = 0, nunit = 0;
+    for (int u = blockIdx.x; u < total; u += gridDim.x) {
+      const Unit un = decode(g, u);
+      if (un.ksteps == 0) continue;       // empty expert: the epilogue writes zeros by itself
+      const uint32_t b = nunit & 1u, tph = (nunit >> 1) & 1u;
+      if (!mbar_wait(sm.tempty(b), tph ^ 1u, sm.abort_flag(), g.status, ST_TIMEOUT_TMEM_EMPTY))
+        break;
+      tc_fence_after_sync();
+      bool ok = true;
+      for (int ks = 0; ks < un.ksteps; ++ks, ++it) {
+        const int s = it % kStages;
+        const uint32_t ph = (it / kStages) & 1u;
+        if (!mbar_wait(sm.full(s), ph, sm.abort_flag(), g.status, ST_TIMEOUT_FULL)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after_sync();
+        // MN-major, 128-byte swizzle: 64-column atoms are kBox bytes apart (LBO), 8-row groups
+        // 1024 bytes apart (SBO); one UMMA (K = 16 rows) spans two groups = 2048 bytes.
+        const uint64_t adesc = umma_desc_mnmajor_sw128(smem_u32(sm.a(s)), kBox, 1024);
+        const uint64_t bdesc = umma_desc_mnmajor_sw128(smem_u32(sm.b(s)), kBox, 1024);
+#pragma unroll
+        for (int j = 0; j < kKS / 16; ++j)
+          umma_f16(tmem_base + b * kTN, adesc + (j * 2048 >> 4), bdesc + (j * 2048 >> 4), idesc,
+                   (ks > 0 || j > 0) ? 1u : 0u);
+        umma_commit(sm.empty(s));
+      }
+      if (!ok) break;
+      umma_commit(sm.tfull(b));
+      ++nunit;
+    }
+  } else if (warp >= 4) {
+    // ---------------------------------------------------------------- epilogue (8 warps)
+    const int ew = warp - 4;
+    const int q = ew & 3, half = ew >> 2;
+    const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
+    uint32_t nunit = 0;
+    for (int u = blockIdx.x; u < total; u += gridDim.x) {
+      const Unit un = decode(g, u);
+      const int m = un.mt * kTM + q * 32 + lane;
+      const int n0 = un.nt * kTN + half * 128;
+      __nv_bfloat16* dst = g.out + (static_cast<long long>(un.e) * g.M + m) * g.N + n0;
+      if (un.ksteps == 0) {
+        if (m < g.M) {
+          for (int i = 0; i < 128; i += 8)
+            if (n0 + i < g.N) *reinterpret_cast<uint4*>(dst + i) = make_uint4(0u, 0u, 0u, 0u);
+        }
+        continue;
+      }
+      const uint32_t b = nunit & 1u, tph = (nunit >> 1) & 1u;
+      if (!mbar_wait(sm.tfull(b), tph, sm.abort_flag(), g.status, ST_TIMEOUT_TMEM_FULL)) break;
+      tc_fence_after_sync();
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        uint32_t v[16];
+        tmem_ld_32x32b_x16(lane_base + b * kTN + half * 128 + c * 16, v);
+        tmem_ld_wait_x16(v);
+        if (m < g.M) {
+#pragma unroll
+          for (int i = 0; i < 16; i += 8) {
+            if (n0 + c * 16 + i < g.N) {
+              uint4 o;
+              __nv_bfloat162 p;
+              p = __floats2bfloat162_rn(__uint_as_float(v[i]), __uint_as_float(v[i + 1]));
+              o.x = *reinterpret_cast<uint32_t*>(&p);
+              p = __floats2bfloat162_rn(__uint_as_float(v[i + 2]), __uint_as_float(v[i + 3]));
+              o.y = *reinterpret_cast<uint32_t*>(&p);
+              p = __floats2bfloat162_rn(__uint_as_float(v[i + 4]), __uint_as_float(v[i + 5]));
+              o.z = *reinterpret_cast<uint32_t*>(&p);
+              p = __floats2bfloat162_rn(__uint_as_float(v[i + 6]), __uint_as_float(v[i + 7]));
+              o.w = *reinterpret_cast<uint32_t*>(&p);
+              *reinterpret_cast<uint4*>(dst + c * 16 + i) = o;
+            }
+          }
+        }
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(sm.tempty(b));
+      ++nunit;
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  if (*sm.abort_flag()) {
+    for (int i = 0; i < 64; ++i) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) tmem_dealloc(tmem_base, 512);
+}
+
+}  // namespace wgrad
+}  // namespace nv41
+
+using namespace nv41;
+
+extern "C" int nv41_moe_wgrad_bf16(const void* a_rows, const void* b_rows, const int* pad_off,
+                                   int E, int M, int N, long long P_max, void* out,
+                                   unsigned* status, void* stream) {
+  if (!a_rows || !b_rows || !pad_off || !out || !status || E <= 0 || M <= 0 || N <= 0 ||
+      P_max <= 0 || (P_max % 128) != 0)
+    return NV41_ERR_INVALID;
+  if ((M % 8) != 0 || (N % 8) != 0) return NV41_ERR_UNSUPPORTED;
+  wgrad::Args g;
+  memset(&g, 0, sizeof(g));
+  int rc = make_tmap_2d(&g.tmap_a, a_rows, static_cast<unsigned long long>(P_max), M, 2, 64, 64);
+  if (rc != NV41_OK) return rc;
+  rc = make_tmap_2d(&g.tmap_b, b_rows, static_cast<unsigned long long>(P_max), N, 2, 64, 64);
+  if (rc != NV41_OK) return rc;
+  g.pad_off = pad_off;
+  g.out = static_cast<__nv_bfloat16*>(out);
+  g.E = E;
+  g.M = M;
+  g.N = N;
+  g.tiles_m = (M + wgrad::kTM - 1) / wgrad::kTM;
+  g.tiles_n = (N + wgrad::kTN - 1) / wgrad::kTN;
+  g.status = status;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(wgrad::wgrad_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             wgrad::kSmemBytes) != cudaSuccess)
+      return NV41_ERR_CUDA;
+    configured = true;
+  }
+  const long long units = static_cast<long long>(E) * g.tiles_m * g.tiles_n;
+  int grid = sm_count();
+  if (units < grid) grid = static_cast<int>(units);
+  wgrad::wgrad_kernel<<<grid, wgrad::kThreads, wgrad::kSmemBytes,
+                        static_cast<cudaStream_t>(stream)>>>(g);
+  return launch_status();
+}

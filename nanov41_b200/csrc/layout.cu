@@ -171,9 +171,10 @@ layout_scatter_kernel(const void* __restrict__ idx, int is_i64,
 }
 
 // One warp per token; 16-byte loads of bf16 rows, fp32 accumulation in slot order.
+template <bool kOutFp32>
 __global__ void __launch_bounds__(256)
 combine_topk_kernel(const __nv_bfloat16* __restrict__ y_rows, const int* __restrict__ row_of_flat,
-                    const __nv_bfloat16* __restrict__ shared_out, __nv_bfloat16* __restrict__ out,
+                    const __nv_bfloat16* __restrict__ shared_out, void* __restrict__ out_v,
                     long long T, int k, int D) {
   const int lane = threadIdx.x & 31;
   const long long warp0 = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
@@ -205,13 +206,20 @@ combine_topk_kernel(const __nv_bfloat16* __restrict__ y_rows, const int* __restr
           acc[2 * i + 1] += __uint_as_float(w[i] & 0xFFFF0000u);
         }
       }
-      uint32_t o[4];
+      if (kOutFp32) {
+        float* out = static_cast<float*>(out_v) + t * D + c * 8;
+        *reinterpret_cast<float4*>(out) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+        *reinterpret_cast<float4*>(out + 4) = make_float4(acc[4], acc[5], acc[6], acc[7]);
+      } else {
+        uint32_t o[4];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const __nv_bfloat162 b = __floats2bfloat162_rn(acc[2 * i], acc[2 * i + 1]);
-        o[i] = *reinterpret_cast<const uint32_t*>(&b);
+        for (int i = 0; i < 4; ++i) {
+          const __nv_bfloat162 b = __floats2bfloat162_rn(acc[2 * i], acc[2 * i + 1]);
+          o[i] = *reinterpret_cast<const uint32_t*>(&b);
+        }
+        *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(out_v) + t * D + c * 8) =
+            make_uint4(o[0], o[1], o[2], o[3]);
       }
-      *reinterpret_cast<uint4*>(out + t * D + c * 8) = make_uint4(o[0], o[1], o[2], o[3]);
     }
   }
 }
@@ -312,18 +320,22 @@ extern "C" int nv41_moe_layout_build_static(const void* expert_idx, int idx_is_i
 }
 
 extern "C" int nv41_moe_combine(const void* y_rows_bf16, const int* row_of_flat,
-                                const void* shared_bf16, void* out_bf16, long long T, int k,
-                                int D, void* stream) {
-  if (!y_rows_bf16 || !row_of_flat || !out_bf16 || T < 0 || k <= 0 || D <= 0 || (D % 8) != 0)
+                                const void* shared_bf16, void* out, int out_is_fp32, long long T,
+                                int k, int D, void* stream) {
+  if (!y_rows_bf16 || !row_of_flat || !out || T < 0 || k <= 0 || D <= 0 || (D % 8) != 0)
     return NV41_ERR_INVALID;
   if (T == 0) return NV41_OK;
   long long blocks = (T + 7) / 8;
   const long long cap = 148LL * 16;
   if (blocks > cap) blocks = cap;
-  combine_topk_kernel<<<static_cast<unsigned>(blocks), 256, 0,
-                        static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __nv_bfloat16*>(y_rows_bf16), row_of_flat,
-      static_cast<const __nv_bfloat16*>(shared_bf16), static_cast<__nv_bfloat16*>(out_bf16), T,
-      k, D);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const __nv_bfloat16* y = static_cast<const __nv_bfloat16*>(y_rows_bf16);
+  const __nv_bfloat16* sh = static_cast<const __nv_bfloat16*>(shared_bf16);
+  if (out_is_fp32)
+    combine_topk_kernel<true><<<static_cast<unsigned>(blocks), 256, 0, st>>>(y, row_of_flat, sh,
+                                                                              out, T, k, D);
+  else
+    combine_topk_kernel<false><<<static_cast<unsigned>(blocks), 256, 0, st>>>(y, row_of_flat, sh,
+                                                                               out, T, k, D);
   return launch_status();
 }

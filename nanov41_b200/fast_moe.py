@@ -1,0 +1,237 @@
+"""Drop-in for ``nanov41.fast_moe`` (nanov41/fast_moe.py) on B200: same module surface
+(``fast_moe_forward``, ``install``/``uninstall``, ``configure``, ``path_for``, ``graph_safe``,
+static-routing helpers, sync auditors, and the private helpers the reference's tests reach into),
+with the routed experts running in the FP8 tcgen05 path of libnanov41_b200.so.
+
+Usage is the reference's:  ``import nanov41_b200.fast_moe as fast_moe; fast_moe.install(M)``.
+The router (``self.gate``) and the shared expert stay the caller's torch modules; the shared
+expert's output is added in fp32 inside the combine kernel, so there is a single bf16 rounding
+as in nanov41/fast_moe.py:311-338,467-474.
+"""
+from __future__ import annotations
+
+import contextlib
+import os
+import threading
+
+import torch
+from torch.utils._python_dispatch import TorchDispatchMode
+
+from . import autograd_moe, ops
+
+_GROUPED_MM = None            # the torch._grouped_mm path does not exist in this build
+_VALID_SCATTER = ("auto", "index_add", "scatter_add", "permute")
+
+
+def _env_flag(name: str, default: bool) -> bool:
+    raw = os.environ.get(name)
+    if raw is None:
+        return default
+    return raw.strip().lower() not in ("", "0", "false", "off", "no")
+
+
+# The knobs of nanov41/fast_moe.py:116-120 are accepted and validated, but they select between
+# torch code paths that this build does not have: there is one path (the CUDA library).
+FORCE_LOOP = _env_flag("NANOV41_MOE_FORCE_LOOP", False)
+FUSE_W13 = _env_flag("NANOV41_MOE_FUSE_W13", True)
+SCATTER_MODE = (os.environ.get("NANOV41_MOE_SCATTER", "auto") or "auto").strip().lower()
+if SCATTER_MODE not in _VALID_SCATTER:
+    raise ValueError(f"NANOV41_MOE_SCATTER must be one of {_VALID_SCATTER}, got {SCATTER_MODE!r}")
+
+
+def configure(*, force_loop: bool | None = None, scatter: str | None = None,
+              fuse_w13: bool | None = None) -> None:
+    """nanov41/fast_moe.py:123-135: same validation (ValueError on a bad ``scatter``)."""
+    global FORCE_LOOP, SCATTER_MODE, FUSE_W13
+    if force_loop is not None:
+        FORCE_LOOP = bool(force_loop)
+    if scatter is not None:
+        scatter = scatter.strip().lower()
+        if scatter not in _VALID_SCATTER:
+            raise ValueError(f"scatter must be one of {_VALID_SCATTER}, got {scatter!r}")
+        SCATTER_MODE = scatter
+    if fuse_w13 is not None:
+        FUSE_W13 = bool(fuse_w13)
+
+
+def _world_size(moe) -> int:
+    return moe.n_routed_experts // moe.n_local_experts
+
+
+def _grouped_mm_ready(moe, x: torch.Tensor) -> bool:
+    """Always False: there is no torch._grouped_mm path here (nanov41/fast_moe.py:151-165)."""
+    return False
+
+
+def path_for(moe, x: torch.Tensor) -> str:
+    """Which implementation ``fast_moe_forward`` uses for (moe, x)."""
+    return "tcgen05_fp8"
+
+
+def probe_grouped_mm_capture(device=None) -> tuple[bool, str]:
+    return False, "torch._grouped_mm is not used by the B200 path"
+
+
+def graph_safe(moe=None, x: torch.Tensor | None = None, verify: bool = False) -> bool:
+    """The path launches a fixed kernel sequence with shapes that depend only on (T, k, D, I, E)
+    and never reads a device value on the host."""
+    return torch.cuda.is_available()
+
+
+_STATIC_ATTR = "_fast_moe_static_sizes"
+
+
+def _static_sizes(moe):
+    return getattr(moe, _STATIC_ATTR, None)
+
+
+def _count_experts(flat: torch.Tensor, n_experts: int) -> torch.Tensor:
+    """nanov41/fast_moe.py:289-293: per-expert histogram, int64 [E], no host round trip."""
+    lay = ops.build_layout(flat.reshape(-1), n_experts, 1)
+    return lay.counts.to(torch.int64)
+
+
+def _sort_tokens(indices: torch.Tensor, n_experts: int):
+    """nanov41/fast_moe.py:296-308: (order [R], tok [R], counts [E]) of the stable expert-major
+    ordering, computed by the layout kernels."""
+    _, k = indices.shape
+    lay = ops.build_layout(indices.reshape(-1), n_experts, k)
+    order = lay.order.to(torch.int64)
+    return order, torch.div(order, k, rounding_mode="floor"), lay.counts.to(torch.int64)
+
+
+def _scatter_topk(outs, tok, order, T: int, k: int, dim: int, mode: str | None = None):
+    """nanov41/fast_moe.py:311-338: sum the k per-slot rows (sorted order) into fp32 [T, dim]."""
+    if mode is not None and mode not in _VALID_SCATTER:
+        raise ValueError(f"scatter must be one of {_VALID_SCATTER}, got {mode!r}")
+    if outs.dtype != torch.bfloat16:
+        raise ops.Nv41Error("_scatter_topk: the CUDA combine takes bf16 rows")
+    row_of_flat = torch.empty(T * k, dtype=torch.int32, device=outs.device)
+    row_of_flat[order] = torch.arange(T * k, dtype=torch.int32, device=outs.device)
+    return ops.combine(outs.contiguous(), row_of_flat, T, k, out_fp32=True)
+
+
+def record_group_sizes(moe, x: torch.Tensor, image_mask: torch.Tensor | None = None) -> list[int]:
+    """nanov41/fast_moe.py:247-260 (the one host sync of the static-routing workflow)."""
+    xf = x.view(-1, moe.dim)
+    mask = None if image_mask is None else image_mask.flatten()
+    with torch.no_grad():
+        _, indices = moe.gate(xf, mask)
+    counts = _count_experts(indices.reshape(-1), moe.n_routed_experts).tolist()
+    if sum(counts) != indices.numel():
+        raise RuntimeError(f"group sizes {sum(counts)} != rows {indices.numel()}")
+    return counts
+
+
+def install_static_routing(moe, sizes) -> tuple[int, ...]:
+    """nanov41/fast_moe.py:263-278: same validation.  The sizes are recorded but not needed:
+    the layout is always built on the device."""
+    if moe.n_local_experts != moe.n_routed_experts:
+        raise ValueError("static routing supports world_size == 1 only")
+    sizes = tuple(int(c) for c in sizes)
+    if len(sizes) != moe.n_local_experts:
+        raise ValueError(f"expected {moe.n_local_experts} group sizes, got {len(sizes)}")
+    if any(c < 0 for c in sizes):
+        raise ValueError(f"negative group size in {sizes}")
+    setattr(moe, _STATIC_ATTR, sizes)
+    return sizes
+
+
+def uninstall_static_routing(moe):
+    sizes = _static_sizes(moe)
+    if sizes is not None:
+        delattr(moe, _STATIC_ATTR)
+    return sizes
+
+
+# ------------------------------------------------------------------------------------ forward
+def fast_moe_forward(self, x: torch.Tensor, image_mask: torch.Tensor | None = None) -> torch.Tensor:
+    """Drop-in replacement for ``_ref_patched_model.MoE.forward`` (nanov41/fast_moe.py:453-474).
+
+    x: [..., dim] bf16 on CUDA; returns ``y.type_as(x).view(x.shape)``."""
+    if _world_size(self) != 1:
+        raise ops.Nv41Error("fast_moe_forward: sharded experts go through nanov41_b200.ep")
+    shape = x.size()
+    xf = x.view(-1, self.dim)
+    mask = None if image_mask is None else image_mask.flatten()
+    weights, indices = self.gate(xf, mask)
+    shared = self.shared_experts(xf)
+    y = autograd_moe.routed_experts(self, xf, weights, indices, shared)
+    return y.type_as(x).view(shape)
+
+
+def install(M):
+    """``M.MoE.forward = fast_moe_forward``; returns the previous forward (fast_moe.py:478-488)."""
+    target = M.MoE
+    previous = target.forward
+    target.forward = fast_moe_forward
+    return previous
+
+
+def uninstall(M, previous) -> None:
+    M.MoE.forward = previous
+
+
+# ------------------------------------------------------------------------------- sync audit
+_SYNC_OPS = ("_local_scalar_dense", "nonzero", "masked_select", "unique", "bincount",
+             "_unique2", "unique_dim", "unique_consecutive")
+_AUDIT_LOCK = threading.Lock()
+
+
+class _SyncAudit(TorchDispatchMode):
+    """Records (or rejects) aten ops that read a device value on the host or produce a
+    data-dependent shape -- the op list of nanov41/fast_moe.py:496-530."""
+
+    def __init__(self, raise_on_sync: bool):
+        super().__init__()
+        self.raise_on_sync = raise_on_sync
+        self.hits: list[str] = []
+
+    def __torch_dispatch__(self, func, types, args=(), kwargs=None):
+        name = func.overloadpacket.__name__ if hasattr(func, "overloadpacket") else str(func)
+        if name in _SYNC_OPS:
+            self.hits.append(name)
+            if self.raise_on_sync:
+                raise AssertionError(f"host sync / dynamic shape op inside MoE forward: {name}")
+        return func(*args, **(kwargs or {}))
+
+
+@contextlib.contextmanager
+def _patched_host_reads(audit: _SyncAudit):
+    names = ("tolist", "item", "cpu", "numpy")
+    saved = {n: getattr(torch.Tensor, n) for n in names}
+
+    def wrap(n):
+        def f(self, *a, **k):
+            if self.is_cuda:
+                audit.hits.append(f"Tensor.{n}")
+                if audit.raise_on_sync:
+                    raise AssertionError(f"host read inside MoE forward: Tensor.{n}")
+            return saved[n](self, *a, **k)
+        return f
+
+    for n in names:
+        setattr(torch.Tensor, n, wrap(n))
+    try:
+        yield
+    finally:
+        for n in names:
+            setattr(torch.Tensor, n, saved[n])
+
+
+@contextlib.contextmanager
+def assert_no_sync():
+    """Raise AssertionError on any host sync inside the block (nanov41/fast_moe.py:550-578)."""
+    with _AUDIT_LOCK:
+        audit = _SyncAudit(True)
+        with _patched_host_reads(audit), audit:
+            yield audit
+
+
+@contextlib.contextmanager
+def audit_no_sync():
+    """Like ``assert_no_sync`` but only records: ``audit.hits`` lists the offenders."""
+    with _AUDIT_LOCK:
+        audit = _SyncAudit(False)
+        with _patched_host_reads(audit), audit:
+            yield audit

@@ -192,17 +192,19 @@ def build_layout(flat_expert: torch.Tensor, n_experts: int, k: int,
 
 
 def combine(y_rows: torch.Tensor, row_of_flat: torch.Tensor, T: int, k: int,
-            shared: torch.Tensor | None = None) -> torch.Tensor:
-    """out[t] = bf16(sum_j fp32(y_rows[row_of_flat[t*k+j]]) + fp32(shared[t]))."""
+            shared: torch.Tensor | None = None, out_fp32: bool = False) -> torch.Tensor:
+    """out[t] = bf16(sum_j fp32(y_rows[row_of_flat[t*k+j]]) + fp32(shared[t])); with
+    ``out_fp32`` the unrounded fp32 sum is returned."""
     _need_cuda(y_rows, row_of_flat, shared)
     D = y_rows.shape[1]
     if y_rows.dtype != torch.bfloat16 or not y_rows.is_contiguous():
         raise Nv41Error("combine expects contiguous bf16 rows")
     if shared is not None:
         shared = shared.to(torch.bfloat16).contiguous()
-    out = torch.empty((T, D), dtype=torch.bfloat16, device=y_rows.device)
+    out = torch.empty((T, D), dtype=torch.float32 if out_fp32 else torch.bfloat16,
+                      device=y_rows.device)
     check(_lib.load().nv41_moe_combine(_ptr(y_rows), _ptr(row_of_flat), _ptr(shared), _ptr(out),
-                                       T, k, D, _stream()), "nv41_moe_combine")
+                                       int(out_fp32), T, k, D, _stream()), "nv41_moe_combine")
     return out
 
 
@@ -270,15 +272,67 @@ class Fp8ExpertWeights:
     E: int
     I: int
     D: int
+    w13_codes_t: torch.Tensor | None = None   # uint8 [E, Dpad, 2I]  (backward: dX GEMM)
+    w2_codes_t: torch.Tensor | None = None    # uint8 [E, Ipad, Dpad] (backward: dact GEMM)
 
 
-def quantize_expert_weights(w1: torch.Tensor, w3: torch.Tensor, w2: torch.Tensor) -> Fp8ExpertWeights:
-    """w1, w3: bf16 [E, I, D]; w2: bf16 [E, D, I] (the [out, in] orientation Linear stores)."""
+def quantize_expert_weights(w1: torch.Tensor, w3: torch.Tensor, w2: torch.Tensor,
+                            transposed: bool = False) -> Fp8ExpertWeights:
+    """w1, w3: bf16 [E, I, D]; w2: bf16 [E, D, I] (the [out, in] orientation Linear stores).
+    ``transposed`` also produces the transposed code copies the backward GEMMs read."""
     E, I, D = w1.shape
     w13 = torch.cat((w1, w3), dim=1).contiguous()
-    c13, s13 = quant_fp8_128x128(w13)
-    c2, s2 = quant_fp8_128x128(w2.contiguous())
-    return Fp8ExpertWeights(c13, s13, c2, s2, E, I, D)
+    r13 = quant_fp8_128x128(w13, transposed)
+    r2 = quant_fp8_128x128(w2.contiguous(), transposed)
+    return Fp8ExpertWeights(r13[0], r13[1], r2[0], r2[1], E, I, D,
+                            r13[2] if transposed else None, r2[2] if transposed else None)
+
+
+def gather_rows(src: torch.Tensor, rows: torch.Tensor) -> torch.Tensor:
+    """dst[p] = src[rows[p]] (zero row where rows[p] < 0); bf16 [n, cols] -> [len(rows), cols]."""
+    _need_cuda(src, rows)
+    if src.dtype != torch.bfloat16 or src.dim() != 2 or src.stride(1) != 1:
+        raise Nv41Error("gather_rows expects a 2-D bf16 tensor with unit inner stride")
+    out = torch.empty((rows.numel(), src.shape[1]), dtype=torch.bfloat16, device=src.device)
+    check(_lib.load().nv41_gather_rows_bf16(_ptr(src), src.stride(0), _ptr(rows), rows.numel(),
+                                            src.shape[1], _ptr(out), _stream()),
+          "nv41_gather_rows_bf16")
+    return out
+
+
+def swiglu_bwd_quant(dact: torch.Tensor, gate: torch.Tensor, up: torch.Tensor,
+                     layout: DeviceLayout, limit: float):
+    """SwiGLU backward on [P_max, I] bf16 rows -> (dgate, dup bf16, [dgate|dup] e4m3 codes
+    [P_max, 2I], scales fp32 [2I/128, P_max], dws fp32 [P_max])."""
+    _need_cuda(dact, gate, up)
+    P, I = dact.shape
+    dev = dact.device
+    dgate = torch.empty_like(dact)
+    dup = torch.empty_like(dact)
+    codes = torch.empty((P, 2 * I), dtype=torch.uint8, device=dev)
+    scales = torch.empty((2 * I // 128, P), dtype=torch.float32, device=dev)
+    dws = torch.zeros(P, dtype=torch.float32, device=dev)
+    check(_lib.load().nv41_swiglu_bwd_quant(_ptr(dact), _ptr(gate), _ptr(up),
+                                            _ptr(layout.row_weight), _ptr(layout.meta), I, P,
+                                            float(limit), _ptr(dgate), _ptr(dup), _ptr(codes),
+                                            _ptr(scales), _ptr(dws), _stream()),
+          "nv41_swiglu_bwd_quant")
+    return dgate, dup, codes, scales, dws
+
+
+def wgrad_bf16(a_rows: torch.Tensor, b_rows: torch.Tensor, layout: DeviceLayout) -> torch.Tensor:
+    """out[e] = a_rows[rows of e]^T @ b_rows[rows of e]: bf16 [P_max, M], [P_max, N] -> [E, M, N]."""
+    _need_cuda(a_rows, b_rows)
+    P, M = a_rows.shape
+    N = b_rows.shape[1]
+    if not (a_rows.is_contiguous() and b_rows.is_contiguous()) or b_rows.shape[0] != P:
+        raise Nv41Error("wgrad_bf16 expects contiguous [P_max, *] bf16 operands")
+    out = torch.empty((layout.E, M, N), dtype=torch.bfloat16, device=a_rows.device)
+    st = status_word(a_rows.device)
+    check(_lib.load().nv41_moe_wgrad_bf16(_ptr(a_rows), _ptr(b_rows), _ptr(layout.pad_off),
+                                          layout.E, M, N, P, _ptr(out), _ptr(st), _stream()),
+          "nv41_moe_wgrad_bf16")
+    return out
 
 
 def moe_forward_fp8(x: torch.Tensor, wq: Fp8ExpertWeights, weights: torch.Tensor,

@@ -136,3 +136,69 @@ def rel_errors(a: torch.Tensor, ref: torch.Tensor):
     if scale == 0:
         return d.max().item(), d.mean().item()
     return d.max().item() / scale, d.mean().item() / scale
+
+
+def swiglu_bwd(dact, gate, up, w, limit):
+    """nanov41/triton_grouped_moe.py:783-792 (_swiglu_bwd_kernel maths, strict clamp masks on the
+    clamped values) and :1251-1261 (_moe_dws_kernel).  fp32 in/out:
+    returns (dgate, dup, dws_row)."""
+    gc, uc = gate, up
+    mg = torch.ones_like(gate, dtype=torch.bool)
+    mu = torch.ones_like(up, dtype=torch.bool)
+    if limit is not None and limit > 0:
+        gc = torch.clamp(gate, max=limit)
+        uc = torch.clamp(up, min=-limit, max=limit)
+        mg, mu = gc < limit, uc.abs() < limit
+    sig = torch.sigmoid(gc)
+    silu = gc * sig
+    dsilu = sig * (1 + gc * (1 - sig))
+    dw = dact * w
+    dgate = torch.where(mg, dw * uc * dsilu, torch.zeros_like(dw))
+    dup = torch.where(mu, dw * silu, torch.zeros_like(dw))
+    dws = (dact * (silu * uc)).sum(-1)
+    return dgate, dup, dws
+
+
+def moe_fp8_backward(x, dout, weights, indices, limit, prepared, parts):
+    """Oracle of the FP8 expert-path backward, mirroring the data flow of
+    nanov41/triton_grouped_moe.py:1461-1483 (_GroupedMoEv2FP8.backward) with 1x128 / 128x128
+    block scales: dact and dX through dequantised FP8 operands (fp32 matmul), dW in bf16 operands
+    with fp32 accumulation.  ``parts`` = the dict returned by moe_fp8(return_parts=True).
+    Returns dict(dx [T,D] bf16, dws [T,k] fp32, dw1, dw3 [E,I,D], dw2 [E,D,I] bf16)."""
+    T, k = indices.shape
+    E, I, D = prepared["E"], prepared["I"], prepared["D"]
+    w13d, w2d = prepared["w13d"], prepared["w2d"]
+    order, tok, counts = parts["order"], parts["tok"], parts["counts"]
+    ws = weights.reshape(-1).index_select(0, order)
+    dout = dout.to(torch.bfloat16)
+    dq = Q.fp8_dequant_1x128(*Q.fp8_quant_1x128(dout))[:, :D]
+    R = T * k
+    dx_rows = torch.zeros(R, D, dtype=torch.bfloat16)
+    dws_rows = torch.zeros(R)
+    dw1 = torch.zeros(E, I, D, dtype=torch.bfloat16)
+    dw3 = torch.zeros(E, I, D, dtype=torch.bfloat16)
+    dw2 = torch.zeros(E, D, I, dtype=torch.bfloat16)
+    pos = 0
+    for e in range(E):
+        c = int(counts[e])
+        if c:
+            sl = slice(pos, pos + c)
+            t = tok[sl]
+            dact = (dq[t] @ w2d[e]).to(torch.bfloat16).float()
+            dg, du, dws = swiglu_bwd(dact, parts["gate"][sl].float(), parts["up"][sl].float(),
+                                     ws[sl, None], limit)
+            dg, du = dg.to(torch.bfloat16), du.to(torch.bfloat16)
+            dws_rows[sl] = dws
+            dgu = torch.cat((dg, du), dim=1)
+            dgu_d = Q.fp8_dequant_1x128(*Q.fp8_quant_1x128(dgu))[:, :2 * I]
+            dx_rows[sl] = (dgu_d @ w13d[e]).to(torch.bfloat16)
+            dw2[e] = (dout[t].float().t() @ parts["h"][sl].float()).to(torch.bfloat16)
+            dw1[e] = (dg.float().t() @ x[t].float()).to(torch.bfloat16)
+            dw3[e] = (du.float().t() @ x[t].float()).to(torch.bfloat16)
+        pos += c
+    flat = torch.empty(R, D, dtype=torch.float32)
+    flat.index_copy_(0, order, dx_rows.float())
+    dx = flat.view(T, k, D).sum(1).to(torch.bfloat16)
+    dws_flat = torch.empty(R)
+    dws_flat.index_copy_(0, order, dws_rows)
+    return dict(dx=dx, dws=dws_flat.view(T, k), dw1=dw1, dw3=dw3, dw2=dw2)

@@ -1,0 +1,49 @@
+"""CPU: the C-ABI library loads without a GPU and exports exactly what include/nanov41_b200.h
+declares; the ctypes prototype table covers every declaration.  No compute call is made."""
+import ctypes
+import re
+from pathlib import Path
+
+import pytest
+
+ROOT = Path(__file__).resolve().parent.parent
+HEADER = ROOT / "include" / "nanov41_b200.h"
+
+
+def declared_symbols():
+    text = re.sub(r"/\*.*?\*/", "", HEADER.read_text(), flags=re.S)
+    return sorted(set(re.findall(r"\b(nv41_\w+)\s*\(", text)))
+
+
+def test_header_declares_entry_points():
+    names = declared_symbols()
+    assert "nv41_moe_gemm1_fp8" in names and "nv41_quant_fp8_1x128" in names
+    assert len(names) >= 10
+
+
+def test_library_exports_every_declared_symbol():
+    from nanov41_b200 import _lib
+    lib = _lib.load()
+    for name in declared_symbols():
+        assert isinstance(getattr(lib, name), ctypes._CFuncPtr), name
+    assert sorted(_lib.SIGNATURES) == declared_symbols()
+    assert lib.nv41_abi_version() >= 100
+
+
+def test_argument_validation_needs_no_gpu():
+    from nanov41_b200 import _lib
+    lib = _lib.load()
+    assert lib.nv41_moe_layout_workspace_bytes(1000, 64) == 4 * 64 * 4
+    assert lib.nv41_moe_layout_workspace_bytes(-1, 64) == _lib.ERR_INVALID
+    assert lib.nv41_quant_fp8_1x128(None, 0, None, 5, 128, None, None, 1, 1, None) == _lib.ERR_INVALID
+    assert lib.nv41_quant_nvfp4_1x16(None, 0, 4, 20, 1.0, None, None, None) == _lib.ERR_INVALID
+    assert lib.nv41_moe_combine(None, None, None, None, 0, 4, 2, 64, None) == _lib.ERR_INVALID
+
+
+def test_ops_refuse_cpu_tensors():
+    import torch
+    from nanov41_b200 import ops
+    with pytest.raises(RuntimeError):
+        ops.quant_fp8_128x128(torch.zeros(1, 128, 128, dtype=torch.bfloat16))
+    with pytest.raises(RuntimeError):
+        ops.build_layout(torch.zeros(8, dtype=torch.int64), 4, 2)

@@ -1,0 +1,71 @@
+"""GPU: backward of the FP8 expert path (dact / dX FP8 GEMMs, SwiGLU backward, bf16 tcgen05
+weight-gradient GEMMs) against the oracle; tolerance for bf16 gradients: max rel <= 2e-2,
+mean rel <= 2e-3 of max|ref| (tests/kernel_parity_fast_moe.py:58,68-75 uses 2e-2 for bf16)."""
+import pytest
+import torch
+
+from nanov41_b200.workloads import make_case
+from oracle import moe as OM
+
+pytestmark = pytest.mark.gpu
+LIMIT = 10.0
+CASES = {
+    "tiny_c1": dict(T=128, E=4, k=2, D=64, I=128),
+    "d8": dict(T=512, E=8, k=2, D=256, I=256),
+    "d12": dict(T=700, E=16, k=2, D=384, I=384),
+    "c2_small": dict(T=768, E=8, k=6, D=1024, I=1024),
+    "empty_expert": dict(T=300, E=8, k=2, D=256, I=128, empty_expert=3),
+}
+
+
+@pytest.mark.parametrize("name", list(CASES))
+def test_backward_vs_oracle(name):
+    from nanov41_b200 import autograd_moe, ops
+    case = CASES[name]
+    c = make_case(seed=21, outliers=False, **case)
+    T, D = c["x"].shape
+    gen = torch.Generator().manual_seed(3)
+    dout = (torch.randn(T, D, generator=gen) * 0.1).bfloat16()
+    g = {n: t.cuda() for n, t in c.items()}
+    x = g["x"].clone().requires_grad_(True)
+    ws = g["weights"].clone().requires_grad_(True)
+    w1, w3, w2 = (g[n].clone().requires_grad_(True) for n in ("w1", "w3", "w2"))
+    y = autograd_moe.experts_forward(x, ws, g["indices"], w1, w3, w2, LIMIT)
+    y.backward(dout.cuda())
+    ops.check_status()
+
+    prep = OM.prepare_weights_fp8(c["w1"], c["w3"], c["w2"])
+    yref, parts = OM.moe_fp8(c["x"], None, None, None, c["weights"], c["indices"], LIMIT,
+                             return_parts=True, prepared=prep)
+    ref = OM.moe_fp8_backward(c["x"], dout, c["weights"], c["indices"], LIMIT, prep, parts)
+    mx, mean = OM.rel_errors(y.detach().cpu(), yref)
+    assert mx <= 2e-2 and mean <= 2e-3
+    for nm, got in (("dx", x.grad), ("dws", ws.grad), ("dw1", w1.grad), ("dw3", w3.grad),
+                    ("dw2", w2.grad)):
+        mx, mean = OM.rel_errors(got.cpu(), ref[nm])
+        assert mx <= 2e-2 and mean <= 2e-3, (nm, mx, mean)
+    if "empty_expert" in case:
+        e = case["empty_expert"]
+        assert torch.all(w1.grad[e] == 0) and torch.all(w2.grad[e] == 0)
+
+
+def test_wgrad_kernel_exact_on_small_integers():
+    """The weight-gradient GEMM with operands whose products and sums are exact in fp32/bf16:
+    the result must equal the integer matmul exactly (pins the MN-major operand layout)."""
+    from nanov41_b200 import ops
+    gen = torch.Generator().manual_seed(0)
+    T, E, k, M, N = 500, 4, 2, 192, 320
+    idx = torch.stack([torch.randperm(E, generator=gen)[:k] for _ in range(T)]).cuda()
+    lay = ops.build_layout(idx.reshape(-1), E, k)
+    P = lay.P_max
+    a = torch.randint(-2, 3, (P, M), generator=gen).bfloat16()
+    b = torch.randint(-2, 3, (P, N), generator=gen).bfloat16()
+    pad = lay.row_token.cpu() < 0
+    a[pad] = 0
+    b[pad] = 0
+    out = ops.wgrad_bf16(a.cuda(), b.cuda(), lay).cpu()
+    ops.check_status()
+    po = lay.pad_off.cpu().tolist()
+    for e in range(E):
+        ref = a[po[e]:po[e + 1]].float().t() @ b[po[e]:po[e + 1]].float()
+        assert torch.equal(out[e].float(), ref.bfloat16().float()), e
