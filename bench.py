@@ -133,6 +133,107 @@ def workload_config():
 
 
 # ------------------------------------------------------------------------------ ours
+def c5_config(world):
+    return {"workload": "config5: expert-parallel FP8 MoE forward, E=256 top-8 uniform-random "
+                        "logits seed 2, D=2048 I=1024, 131072 tokens per step over the box",
+            "E": 256, "T": 131072, "k": 8, "D": 2048, "I": 1024,
+            "parallelism": f"ep{world} (experts sharded, tokens data-parallel, NCCL all-to-all "
+                           "dispatch of fp8 rows / combine of bf16 rows)",
+            "l2": "inputs_exceed_l2", "weights": "block-quantised once outside the timed region"}
+
+
+def run_ep(args, world, rank, local, dev):
+    """N > 1: BASELINE config 5, strong scaling (131072 tokens per step over the box)."""
+    import torch.distributed as dist
+    from nanov41_b200 import ep, ops
+    from nanov41_b200.workloads import C5
+
+    E, k, D, I = C5["E"], C5["k"], C5["D"], C5["I"]
+    T = C5["T"] // world
+    e_local = E // world
+    gen = torch.Generator(device=dev)
+
+    def expert_weight(e, shape, fan_in, salt):
+        gen.manual_seed(1_000_003 * salt + e)          # per expert id: same experts at any N
+        return (torch.randn(shape, generator=gen, device=dev) * fan_in ** -0.5).bfloat16()
+
+    ids = range(rank * e_local, (rank + 1) * e_local)
+    w1 = torch.stack([expert_weight(e, (I, D), D, 1) for e in ids])
+    w3 = torch.stack([expert_weight(e, (I, D), D, 2) for e in ids])
+    w2 = torch.stack([expert_weight(e, (D, I), I, 3) for e in ids])
+    wq = ops.quantize_expert_weights(w1, w3, w2)
+    del w1, w3, w2
+    gen.manual_seed(C5["seed"] * 7919 + rank)
+    x = torch.randn(T, D, generator=gen, device=dev).bfloat16()
+    logits = torch.randn(T, E, generator=gen, device=dev)
+    indices = logits.topk(k, dim=-1)[1]
+    weights = torch.rand(T, k, generator=gen, device=dev) + 0.05
+    weights = (weights / weights.sum(-1, keepdim=True) * 1.5).float()
+    x_host = x.cpu().pin_memory()
+    idx_host = indices.cpu().pin_memory()
+    w_host = weights.cpu().pin_memory()
+    out_host = torch.empty((T, D), dtype=torch.bfloat16).pin_memory()
+
+    def step_device():
+        return ep.moe_forward_fp8_ep(x, wq, weights, indices, E, LIMIT)
+
+    def step_e2e():
+        xd = x_host.to(dev, non_blocking=True)
+        idd = idx_host.to(dev, non_blocking=True)
+        wd = w_host.to(dev, non_blocking=True)
+        out_host.copy_(ep.moe_forward_fp8_ep(xd, wq, wd, idd, E, LIMIT), non_blocking=True)
+
+    def timed(fn, steps, warmup):
+        for _ in range(warmup):
+            fn()
+        dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        dist.barrier()
+        torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1)], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return t.item() / steps
+
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    ms_dev = timed(step_device, args.steps, args.warmup)
+    ms_e2e = timed(step_e2e, args.steps, max(1, args.warmup // 2))
+    clocks = sampler.stop() if rank == 0 else {}
+    ops.check_status()
+    if rank == 0:
+        flops = fwd_flops(C5["T"], k, D, I)
+        peaks = json.loads((ROOT / "MEASURED_PEAKS.json").read_text()) \
+            if (ROOT / "MEASURED_PEAKS.json").exists() else {}
+        bf16_peak = peaks.get("bf16_tflops", 1590.0)
+        tfl = flops / (ms_dev * 1e-3) / 1e12
+        line = {
+            "metric": "expert_gemm_tflops", "value": tfl, "unit": "TFLOP/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_dev,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "fp8_e4m3 (fp32 accumulate, bf16 out)", "data": "synthetic",
+            "config": c5_config(world),
+            "e2e": {"value": flops / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s",
+                    "ms_per_step": ms_e2e,
+                    "h2d_bytes_per_step": x_host.numel() * 2 + idx_host.numel() * 8 + w_host.numel() * 4,
+                    "d2h_bytes_per_step": out_host.numel() * 2},
+            "gpu_launches": world * 14 * args.steps, "clocks": clocks,
+            "roofline": {"bound": "tensor", "kernel": "whole EP step (GEMMs + all-to-all)",
+                         "achieved": tfl / world, "peak": 2.0 * bf16_peak, "unit": "TFLOP/s",
+                         "frac": tfl / world / (2.0 * bf16_peak), "traffic": None,
+                         "peak_note": "per-GPU share of the step vs 2 x measured bf16 burst"},
+            "moe_layer_tokens_per_s": C5["T"] / (ms_dev * 1e-3),
+            "cpu_baseline": None,
+        }
+        print(json.dumps(line), flush=True)
+    dist.destroy_process_group()
+
+
 def run_ours(args):
     import torch.distributed as dist
     from nanov41_b200 import ops
@@ -144,6 +245,7 @@ def run_ours(args):
     dev = torch.device("cuda", local)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
+        return run_ep(args, world, rank, local, dev)
 
     cfg = dict(C2)
     c = make_case(**cfg)

@@ -300,6 +300,13 @@ def gather_rows(src: torch.Tensor, rows: torch.Tensor) -> torch.Tensor:
     return out
 
 
+def gather_rows_bytes(src: torch.Tensor, rows: torch.Tensor) -> torch.Tensor:
+    """Row gather of a uint8 matrix whose row length is a multiple of 16 bytes."""
+    if src.dtype != torch.uint8 or src.shape[1] % 16:
+        raise Nv41Error("gather_rows_bytes expects uint8 rows of a multiple of 16 bytes")
+    return gather_rows(src.view(torch.bfloat16), rows).view(torch.uint8)
+
+
 def swiglu_bwd_quant(dact: torch.Tensor, gate: torch.Tensor, up: torch.Tensor,
                      layout: DeviceLayout, limit: float):
     """SwiGLU backward on [P_max, I] bf16 rows -> (dgate, dup bf16, [dgate|dup] e4m3 codes

@@ -1,0 +1,57 @@
+"""GPU, 2 ranks over NCCL: the expert-parallel forward equals the single-GPU forward bit for bit
+(every routed row goes through the same kernels; only its home changes) and the oracle within
+the GEMM tolerance.  Needs two devices; skipped otherwise."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.gpu
+CASE = dict(T=512, E=8, k=2, D=256, I=256)
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world,
+                            device_id=torch.device("cuda", rank))
+    try:
+        from nanov41_b200 import ep, ops
+        from nanov41_b200.workloads import make_case
+        from oracle import moe as OM
+        c = make_case(seed=4, **CASE)
+        g = {n: t.cuda() for n, t in c.items()}
+        T = CASE["T"] // world
+        sl = slice(rank * T, (rank + 1) * T)
+        w1, w3, w2 = ep.shard_expert_weights(g["w1"], g["w3"], g["w2"], rank, world)
+        wq_local = ops.quantize_expert_weights(w1.contiguous(), w3.contiguous(), w2.contiguous())
+        shared = torch.randn(T, CASE["D"], device="cuda").bfloat16()
+        out = ep.moe_forward_fp8_ep(g["x"][sl], wq_local, g["weights"][sl], g["indices"][sl],
+                                    CASE["E"], 10.0, shared)
+        ops.check_status()
+        wq_all = ops.quantize_expert_weights(g["w1"], g["w3"], g["w2"])
+        single = ops.moe_forward_fp8(g["x"][sl], wq_all, g["weights"][sl], g["indices"][sl], 10.0,
+                                     shared)
+        assert torch.equal(out, single)
+        ref = OM.moe_fp8(c["x"][sl], c["w1"], c["w3"], c["w2"], c["weights"][sl], c["indices"][sl],
+                         10.0, shared=shared.cpu())
+        mx, mean = OM.rel_errors(out.cpu(), ref)
+        assert mx <= 2e-2 and mean <= 2e-3, (mx, mean)
+        dist.barrier()
+    finally:
+        dist.destroy_process_group()
+
+
+def test_ep_forward_two_gpus():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    mp.spawn(_worker, args=(2, _free_port()), nprocs=2, join=True)
