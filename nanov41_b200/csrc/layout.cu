@@ -75,20 +75,33 @@ layout_scan_kernel(int* __restrict__ hist, int n_runs, int E, long long R, int n
                    int* __restrict__ counts, int* __restrict__ cum_excl,
                    int* __restrict__ pad_off, int* __restrict__ tile_expert,
                    int* __restrict__ meta) {
-  extern __shared__ int sh[];          // [E] totals, then [E+1] cum_excl, then [E+1] pad_off
+  extern __shared__ int sh[];   // [E] totals | [E+1] cum_excl | [E+1] pad_off | [nseg*E] partials
   int* tot = sh;
   int* cum = sh + E;
   int* pof = sh + 2 * E + 1;
+  int* part = sh + 3 * E + 2;
+  // The runs are cut into nseg segments so that all threads of the CTA take part: thread
+  // (segment, expert) first sums its segment, the segment sums are scanned per expert, then the
+  // same thread rewrites its segment as exclusive prefixes.
+  const int nseg = (static_cast<int>(blockDim.x) / E) > 0 ? static_cast<int>(blockDim.x) / E : 1;
+  const int seg_len = (n_runs + nseg - 1) / nseg;
+  for (int idx = threadIdx.x; idx < E * nseg; idx += blockDim.x) {
+    const int e = idx % E, sg = idx / E;
+    const int r1 = min(n_runs, (sg + 1) * seg_len);
+    int sum = 0;
+    for (int r = sg * seg_len; r < r1; ++r) sum += hist[static_cast<long long>(r) * E + e];
+    part[sg * E + e] = sum;
+  }
+  __syncthreads();
   for (int e = threadIdx.x; e < E; e += blockDim.x) {
-    int run_sum = 0;
-    for (int r = 0; r < n_runs; ++r) {
-      const long long o = static_cast<long long>(r) * E + e;
-      const int c = hist[o];
-      hist[o] = run_sum;               // exclusive prefix over runs, per expert
-      run_sum += c;
+    int running = 0;
+    for (int sg = 0; sg < nseg; ++sg) {
+      const int t = part[sg * E + e];
+      part[sg * E + e] = running;
+      running += t;
     }
-    tot[e] = run_sum;
-    counts[e] = run_sum;
+    tot[e] = running;
+    counts[e] = running;
   }
   __syncthreads();
   if (threadIdx.x == 0) {
@@ -111,9 +124,18 @@ layout_scan_kernel(int* __restrict__ hist, int n_runs, int E, long long R, int n
     cum_excl[e] = cum[e];
     pad_off[e] = pof[e];
   }
-  // add the expert's sorted start to every (run, e) prefix
-  for (long long o = threadIdx.x; o < static_cast<long long>(n_runs) * E; o += blockDim.x)
-    hist[o] += cum[o % E];
+  // hist[run][e] <- sorted start of (run, e): expert start + runs before it
+  for (int idx = threadIdx.x; idx < E * nseg; idx += blockDim.x) {
+    const int e = idx % E, sg = idx / E;
+    const int r1 = min(n_runs, (sg + 1) * seg_len);
+    int running = part[sg * E + e] + cum[e];
+    for (int r = sg * seg_len; r < r1; ++r) {
+      const long long o = static_cast<long long>(r) * E + e;
+      const int c = hist[o];
+      hist[o] = running;
+      running += c;
+    }
+  }
   // tile -> expert table
   for (int t = threadIdx.x; t < n_tiles_max; t += blockDim.x) {
     const int row = t * 128;
@@ -254,7 +276,7 @@ static int layout_build_impl(const void* expert_idx, int idx_is_i64, const float
   layout_hist_kernel<<<ctas, kWarpsPerCta * 32, sh_warp, st>>>(
       expert_idx, idx_is_i64, R, E, n_runs, hist, P_max, flat_of_row, row_token, row_weight,
       status);
-  layout_scan_kernel<<<1, 1024, (3 * E + 2) * sizeof(int), st>>>(
+  layout_scan_kernel<<<1, 1024, (3 * E + 2 + (1024 / E > 0 ? 1024 / E : 1) * E) * sizeof(int), st>>>(
       hist, n_runs, E, R, n_tiles_max, counts, cum_excl, pad_off, tile_expert, meta);
   if (n_runs > 0) {
     layout_scatter_kernel<<<ctas, kWarpsPerCta * 32, sh_warp, st>>>(
