@@ -165,28 +165,40 @@ __device__ __forceinline__ void role_tma(const GemmArgs& g, const SM& sm, int NS
 }
 
 // ------------------------------------------------------------------------------ UMMA warp
+// One issuing thread.  Its per-K-block instruction stream (two barrier waits, four UMMAs, two
+// commits) is serial and shares the sub-partition's issue slots with promotion warps, so it is
+// kept short: 32-bit shared-memory addresses and descriptors are formed once, per-stage values
+// by one multiply-add.
 template <class SM>
 __device__ __forceinline__ void role_mma(const GemmArgs& g, const SM& sm, uint32_t tmem_base,
                                          int NS) {
   constexpr uint32_t idesc = umma_idesc(kBM, kBN, 0, 0);
-  uint32_t it = 0;
+  const uint32_t full0 = smem_u32(sm.full(0)), empty0 = smem_u32(sm.empty(0));
+  const uint32_t tfull0 = smem_u32(sm.tfull(0)), tempty0 = smem_u32(sm.tempty(0));
+  const uint64_t adesc0 = umma_desc_kmajor_sw128(smem_u32(sm.a(0)));
+  const uint64_t bdesc0 = umma_desc_kmajor_sw128(smem_u32(sm.b(0)));
+  uint32_t it = 0, s = 0, ph = 0;
   NV41_FOR_EACH_UNIT(g, mt, nt, e) {
     for (int kb = 0; kb < g.nkb; ++kb, ++it) {
-      const int s = it % NS;
-      const uint32_t ph = (it / NS) & 1u;
       const uint32_t b = it & 1u, tph = (it >> 1) & 1u;
-      if (!mbar_wait(sm.full(s), ph, sm.abort_flag(), g.status, ST_TIMEOUT_FULL)) return;
-      if (!mbar_wait(sm.tempty(b), tph ^ 1u, sm.abort_flag(), g.status, ST_TIMEOUT_TMEM_EMPTY))
+      if (!mbar_wait_addr(full0 + s * 8, ph, sm.abort_flag(), g.status, ST_TIMEOUT_FULL)) return;
+      if (!mbar_wait_addr(tempty0 + b * 8, tph ^ 1u, sm.abort_flag(), g.status,
+                          ST_TIMEOUT_TMEM_EMPTY))
         return;
       tc_fence_after_sync();
-      const uint64_t adesc = umma_desc_kmajor_sw128(smem_u32(sm.a(s)));
-      const uint64_t bdesc = umma_desc_kmajor_sw128(smem_u32(sm.b(s)));
+      const uint64_t adesc = adesc0 + static_cast<uint64_t>(s * (kStageBytes >> 4));
+      const uint64_t bdesc = bdesc0 + static_cast<uint64_t>(s * (kStageBytes >> 4));
       const uint32_t d = tmem_base + b * kBN;
-#pragma unroll
-      for (int j = 0; j < kBK / 32; ++j)     // UMMA K = 32 bytes; +2 = 32 B in 16-byte units
-        umma_f8f6f4(d, adesc + 2 * j, bdesc + 2 * j, idesc, j > 0 ? 1u : 0u);
-      umma_commit(sm.empty(s));              // smem stage free once these UMMAs have read it
-      umma_commit(sm.tfull(b));              // accumulator buffer ready for promotion
+      umma_f8f6f4_first(d, adesc, bdesc, idesc);
+      umma_f8f6f4_acc(d, adesc + 2, bdesc + 2, idesc);     // +2 = 32 bytes of K
+      umma_f8f6f4_acc(d, adesc + 4, bdesc + 4, idesc);
+      umma_f8f6f4_acc(d, adesc + 6, bdesc + 6, idesc);
+      umma_commit_addr(empty0 + s * 8);      // smem stage free once these UMMAs have read it
+      umma_commit_addr(tfull0 + b * 8);      // accumulator buffer ready for promotion
+      if (++s == static_cast<uint32_t>(NS)) {
+        s = 0;
+        ph ^= 1u;
+      }
     }
   }
 }
@@ -297,7 +309,7 @@ __device__ __forceinline__ void role_promote(const GemmArgs& g, const SM& sm, ui
         s0_n = __ldg(sb0 + (kb + 1) * g.bs_kb);
         s1_n = __ldg(sb1 + (kb + 1) * g.bs_kb);
       }
-      if (!mbar_wait(sm.tfull(b), tph, sm.abort_flag(), g.status, ST_TIMEOUT_TMEM_FULL)) return;
+      if (!mbar_wait<40>(sm.tfull(b), tph, sm.abort_flag(), g.status, ST_TIMEOUT_TMEM_FULL)) return;
       tc_fence_after_sync();
       const uint32_t tb = lane_base + b * kBN;
       // piece c (16 columns): SwiGLU -> gate columns half*64 + 16c (c < 4), up columns
@@ -335,7 +347,7 @@ __device__ __forceinline__ void role_promote(const GemmArgs& g, const SM& sm, ui
       // Round gate/up to bf16 (the Linear output dtype) and hand the tile to the SwiGLU warps:
       // row r = 512 bytes = 32 chunks of 16 B (gate chunks 0..15, up chunks 16..31), chunk j
       // stored at (j ^ (r & 7)) so that rows 8 apart never collide on a bank.
-      if (!mbar_wait(sm.hempty(), (unit & 1u) ^ 1u, sm.abort_flag(), g.status, ST_TIMEOUT_AUX))
+      if (!mbar_wait<100>(sm.hempty(), (unit & 1u) ^ 1u, sm.abort_flag(), g.status, ST_TIMEOUT_AUX))
         return;
       uint8_t* hrow = sm.hand() + row_in_tile * 512;
       const int sw = row_in_tile & 7;
@@ -381,7 +393,7 @@ __device__ __forceinline__ void role_swiglu(const GemmArgs& g, const SM& sm, int
     const float wr = g.row_weight[grow];
     const float L = g.limit;
     const long long ocol = static_cast<long long>(nt) * 128;
-    if (!mbar_wait(sm.hfull(), unit & 1u, sm.abort_flag(), g.status, ST_TIMEOUT_AUX)) return;
+    if (!mbar_wait<200>(sm.hfull(), unit & 1u, sm.abort_flag(), g.status, ST_TIMEOUT_AUX)) return;
     uint32_t hp[64];
     __nv_bfloat162 amax2 = __floats2bfloat162_rn(0.f, 0.f);
 #pragma unroll

@@ -54,6 +54,9 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // Bounded wait.  `abort_flag` lives in shared memory and is set by whichever thread gives up
 // first; everybody else sees it on the next poll and leaves too.  Returns false on abort.
 // The budget is wall-clock (about two seconds of SM cycles), checked every 256 polls.
+// kSleepNs > 0 makes the waiter back off between polls: used by the many-thread roles so that
+// their polling does not take issue slots from the single TMA / UMMA issuing threads.
+template <int kSleepNs = 0>
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity,
                                           volatile uint32_t* abort_flag, uint32_t* status,
                                           uint32_t code) {
@@ -61,7 +64,40 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity,
   const long long t0 = clock64();
   uint32_t polls = 0;
   while (true) {
+    if (kSleepNs > 0) __nanosleep(kSleepNs);
     if (mbar_try_wait(bar, parity)) return true;
+    if ((++polls & 255u) == 0u) {
+      if (*abort_flag) return false;
+      if (clock64() - t0 > 4000000000LL) {
+        *abort_flag = 1u;
+        if (status) atomicCAS(status, 0u, (code << 24) | (blockIdx.x & 0xFFFFFFu));
+        return false;
+      }
+    }
+  }
+}
+
+// Same bounded wait on a barrier given by its 32-bit shared-memory address (no backoff): the
+// form the single UMMA / TMA issuing threads use, whose instruction count is on the critical path.
+__device__ __forceinline__ bool mbar_try_wait_addr(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait_addr(uint32_t bar, uint32_t parity,
+                                               volatile uint32_t* abort_flag, uint32_t* status,
+                                               uint32_t code) {
+  if (mbar_try_wait_addr(bar, parity)) return true;
+  const long long t0 = clock64();
+  uint32_t polls = 0;
+  while (true) {
+    if (mbar_try_wait_addr(bar, parity)) return true;
     if ((++polls & 255u) == 0u) {
       if (*abort_flag) return false;
       if (clock64() - t0 > 4000000000LL) {
@@ -225,6 +261,27 @@ __device__ __forceinline__ void umma_f8f6f4(uint32_t tmem_d, uint64_t adesc, uin
       : "r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// The same with the accumulate flag fixed at compile time (no predicate set-up per issue).
+__device__ __forceinline__ void umma_f8f6f4_first(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc,
+                                                  uint32_t idesc) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, 0, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
+      :
+      : "r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc)
+      : "memory");
+}
+__device__ __forceinline__ void umma_f8f6f4_acc(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc,
+                                                uint32_t idesc) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.eq.b32 p, 0, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
+      :
+      : "r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc)
+      : "memory");
+}
 __device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc,
                                          uint32_t idesc, uint32_t accumulate) {
   asm volatile(
@@ -239,6 +296,12 @@ __device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
                    smem_u32(bar))
+               : "memory");
+}
+
+__device__ __forceinline__ void umma_commit_addr(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                   bar)
                : "memory");
 }
 
