@@ -146,6 +146,36 @@ int nv41_moe_gemm_fp8(int a_mode, const void* a_src, long long a_ld, const float
                       long long P_max, void* c_out, long long c_ld, unsigned* status,
                       void* stream);
 
+/* ---- NVFP4 (block-scaled tcgen05) --------------------------------------------------------- */
+
+/* NVFP4 quantizer producing the operand layout of nv41_moe_gemm_nvfp4: same arithmetic as
+ * nv41_quant_nvfp4_1x16 (experiments/tl_kernels/nvfp4_gemm.py:97-126), K zero-padded to a multiple
+ * of 256 (as quantize_nvfp4's k_pad_to), optional row gather (-1 = zero row), and the scale bytes
+ * in 512-byte atoms: sf[(row/128)*(Kpad/64) + k/64][(row%32)*16 + (row/32%4)*4 + (k/16)%4] -- the
+ * tensor-core counterpart of the reference's sm_120 word swizzle (nvfp4_gemm.py:54-74).
+ * packed: u8 [rows, Kpad/2]; sf_atoms: u8 [ceil(rows/128) * (Kpad/64) * 512] (zero it first when
+ * rows is not a multiple of 128). */
+int nv41_quant_nvfp4_tc(const void* x, int x_is_fp32, long long ld_x, const int* gather_rows,
+                        long long rows, int K, float global_scale, void* packed, void* sf_atoms,
+                        void* stream);
+
+/* SwiGLU on bf16 gate|up rows [P_max, 2I] (nanov41/_ref_patched_model.py:858-868) followed by the
+ * NVFP4 quantisation of h = bf16(w * silu(min(g, L)) * clamp(u, +-L)) / global_scale, in the
+ * layout above (Ipad = I rounded up to 256). */
+int nv41_swiglu_quant_nvfp4(const void* gu_bf16, const float* row_weight, const int* meta, int I,
+                            long long P_max, float swiglu_limit, float global_scale, void* packed,
+                            void* sf_atoms, void* stream);
+
+/* Grouped NVFP4 x NVFP4 GEMM C[rows of expert e] = (A @ B_e^T) * a_global * b_global[e], bf16 out;
+ * tcgen05 kind::mxf4nvf4 with 16-element e4m3 block scales applied by the tensor core.
+ * experiments/tl_kernels/nvfp4_gemm.py:165-241 (nvfp4_gemm), grouped per expert like
+ * nanov41/triton_grouped_moe.py:193-214.  a_packed [P_max, Kpad/2], b_packed [E*N, Kpad/2],
+ * scale atoms as above; Kpad % 256 == 0, N % 128 == 0. */
+int nv41_moe_gemm_nvfp4(const void* a_packed, const void* a_sf, float a_global,
+                        const void* b_packed, const void* b_sf, const float* b_global, int E,
+                        int N, int Kpad, const int* tile_expert, long long P_max, void* c_out,
+                        long long c_ld, unsigned* status, void* stream);
+
 /* ---- backward ------------------------------------------------------------------------------ */
 
 /* dst[p] = src[rows[p]] (a zero row where rows[p] < 0); bf16, cols % 8 == 0.  Materialises the

@@ -1,0 +1,302 @@
+// Grouped NVFP4 x NVFP4 expert GEMM for sm_100a: tcgen05 block-scaled UMMA
+// (kind::mxf4nvf4, 16-element blocks, e4m3 block scales applied by the tensor core), TMA-fed,
+// accumulator resident in TMEM for the whole K loop -- no per-K-block promotion is needed because
+// the hardware applies the block scales; the fp32 per-tensor ("global") scales are applied once in
+// the epilogue.
+//
+// Reference: experiments/tl_kernels/nvfp4_gemm.py:165-241 (_make_nvfp4_gemm_kernel / nvfp4_gemm:
+// both operands quantised with quantize_nvfp4, block-scaled MMA, C = A @ B^T), whose sm_120
+// `T.mma_gemm_blockscaled` tile this replaces; grouped over experts like
+// nanov41/triton_grouped_moe.py:193-214 (_aggemm_kernel: expert per M tile from TILE_E).
+//
+// Operands: packed e2m1 (two per byte, low nibble = even k), K-major, K padded to 256;
+// scale bytes in the 512-byte "atom" order the tensor core's scale copy expects:
+//   sf[row_block][k_group][(r % 32) * 16 + (r / 32 % 4) * 4 + j],  row_block = row / 128,
+//   k_group = k / 64, j = (k / 16) % 4
+// (the order of CUTLASS's Sm1xxBlockScaledBasicChunk K-major atom).  One tcgen05.cp
+// (32x128b.warpx4) moves one atom = the scales of 128 rows x 64 k into 4 TMEM columns.
+//
+// CTA (384 threads): warp 0 TMA producer (A/B tiles + the stage's scale atoms by bulk copy),
+// warp 1 issues scale copies and UMMAs (+ owns TMEM), warps 4-11 epilogue.  Tile 128 x 128,
+// stage = 256 k (128 bytes per row = one swizzle row, four UMMAs of K = 64).  TMEM: two
+// 128-column accumulators (the store of one tile overlaps the next mainloop) + 32 columns of
+// scales.  All mbarrier waits are bounded.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cstdint>
+#include <cstring>
+
+#include "../../include/nanov41_b200.h"
+#include "ptx.cuh"
+#include "tmap.cuh"
+#include "util.cuh"
+
+namespace nv41 {
+namespace fp4 {
+
+constexpr int kTM = 128, kTN = 128;
+constexpr int kStageK = 256;                      // fp4 elements per stage = 128 bytes per row
+constexpr int kABytes = kTM * 128, kBBytes = kTN * 128;
+constexpr int kSfBytes = 4 * 512;                 // 4 k-groups x one 128-row atom
+constexpr int kStageBytes = kABytes + kBBytes + 2 * kSfBytes;   // 36 KiB
+constexpr int kStages = 5;
+constexpr int kThreads = 384;
+constexpr int kSmemBytes = kStages * kStageBytes + (2 * kStages + 4) * 8 + 16 + 1024;
+constexpr uint32_t kColSfa = 256, kColSfb = 272;  // TMEM columns of the scale factors
+
+struct Args {
+  CUtensorMap tmap_a;            // packed A [P_max, Kpad/2] bytes, box 128 x 128
+  CUtensorMap tmap_b;            // packed B [E*N, Kpad/2] bytes, box 128 x 128
+  const uint8_t* sfa;            // [P_max/128][Kpad/64][512]
+  const uint8_t* sfb;            // [E*N/128][Kpad/64][512]
+  const int* tile_expert;        // [P_max/128]
+  const float* b_global;         // [E] per-expert global scale of B
+  float a_global;
+  __nv_bfloat16* out;            // [P_max, ld_out]
+  long long ld_out;
+  int N, n_tiles_m, n_tiles_n, nstage, kgroups;   // kgroups = Kpad / 64
+  uint32_t* status;
+};
+
+struct Smem {
+  uint8_t* base;
+  __device__ uint8_t* a(int s) const { return base + s * kStageBytes; }
+  __device__ uint8_t* b(int s) const { return base + s * kStageBytes + kABytes; }
+  __device__ uint8_t* sfa(int s) const { return base + s * kStageBytes + kABytes + kBBytes; }
+  __device__ uint8_t* sfb(int s) const { return sfa(s) + kSfBytes; }
+  __device__ uint64_t* bars() const { return reinterpret_cast<uint64_t*>(base + kStages * kStageBytes); }
+  __device__ uint64_t* full(int s) const { return bars() + s; }
+  __device__ uint64_t* empty(int s) const { return bars() + kStages + s; }
+  __device__ uint64_t* tfull(int b) const { return bars() + 2 * kStages + b; }
+  __device__ uint64_t* tempty(int b) const { return bars() + 2 * kStages + 2 + b; }
+  __device__ uint32_t* tmem_slot() const { return reinterpret_cast<uint32_t*>(bars() + 2 * kStages + 4); }
+  __device__ volatile uint32_t* abort_flag() const { return tmem_slot() + 1; }
+};
+
+// 1-D bulk copy global -> shared, completion counted in bytes on `bar` (16-byte aligned, size % 16 == 0)
+__device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+      :
+      : "r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar))
+      : "memory");
+}
+// Shared-memory descriptor of one 512-byte scale atom: 32 rows of 16 bytes, no swizzle
+// (8-row core matrices of 128 bytes, 128 bytes apart).
+__device__ __forceinline__ uint64_t sf_desc(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_addr >> 4) & 0x3FFFu);
+  d |= static_cast<uint64_t>(128 >> 4) << 32;      // stride byte offset between core matrices
+  d |= static_cast<uint64_t>(1) << 46;             // descriptor version
+  return d;
+}
+// smem -> TMEM: 32 lanes x 128 bits, replicated to the four lane quarters
+__device__ __forceinline__ void sf_copy(uint32_t taddr, uint64_t desc) {
+  asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(desc) : "memory");
+}
+// Instruction descriptor of kind::mxf4nvf4: e2m1 x e2m1, ue4m3 scales, K-major operands, K = 64
+__host__ __device__ constexpr uint32_t idesc_nvfp4(int M, int N) {
+  return (1u << 7) | (1u << 10) | (static_cast<uint32_t>(N >> 3) << 17) | (0u << 23) |
+         (static_cast<uint32_t>(M >> 4) << 24);
+}
+__device__ __forceinline__ void umma_nvfp4(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc,
+                                           uint32_t idesc, uint32_t tsfa, uint32_t tsfb,
+                                           uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %6, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.block16 [%0], %1, %2, %3, [%4], [%5], p;\n\t}"
+      :
+      : "r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(tsfa), "r"(tsfb), "r"(accumulate)
+      : "memory");
+}
+
+#define NV41_FP4_FOR_EACH_UNIT(g, mt, nt, e)                                                      \
+  for (int w_ = blockIdx.x, total_ = (g).n_tiles_m * (g).n_tiles_n, mt = 0, nt = 0, e = 0;        \
+       w_ < total_; w_ += gridDim.x)                                                              \
+    if ((mt = w_ / (g).n_tiles_n, nt = w_ - mt * (g).n_tiles_n, e = (g).tile_expert[mt]) >= 0)
+
+__global__ void __launch_bounds__(kThreads, 1) nvfp4_gemm_kernel(const __grid_constant__ Args g) {
+  extern __shared__ uint8_t smem_raw[];
+  Smem sm;
+  sm.base = reinterpret_cast<uint8_t*>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(sm.full(s), 1u);
+      mbar_init(sm.empty(s), 1u);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(sm.tfull(b), 1u);
+      mbar_init(sm.tempty(b), 8u);
+    }
+    *sm.abort_flag() = 0u;
+    fence_mbar_init();
+    tma_prefetch_desc(&g.tmap_a);
+    tma_prefetch_desc(&g.tmap_b);
+  }
+  if (warp == 1) {
+    tmem_alloc(sm.tmem_slot(), 512);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *sm.tmem_slot();
+
+  if (warp == 0 && lane == 0) {
+    // ---------------------------------------------------------------- producer
+    uint32_t it = 0;
+    bool ok = true;
+    NV41_FP4_FOR_EACH_UNIT(g, mt, nt, e) {
+      const int brow = e * g.N + nt * kTN;
+      const uint8_t* sfa = g.sfa + static_cast<long long>(mt) * g.kgroups * 512;
+      const uint8_t* sfb = g.sfb + static_cast<long long>(brow / 128) * g.kgroups * 512;
+      for (int ks = 0; ks < g.nstage && ok; ++ks, ++it) {
+        const int s = it % kStages;
+        const uint32_t ph = (it / kStages) & 1u;
+        ok = mbar_wait(sm.empty(s), ph ^ 1u, sm.abort_flag(), g.status, ST_TIMEOUT_EMPTY);
+        if (!ok) break;
+        mbar_arrive_expect_tx(sm.full(s), kStageBytes);
+        tma_load_2d(sm.a(s), &g.tmap_a, ks * 128, mt * kTM, sm.full(s));
+        tma_load_2d(sm.b(s), &g.tmap_b, ks * 128, brow, sm.full(s));
+        bulk_load(sm.sfa(s), sfa + ks * kSfBytes, kSfBytes, sm.full(s));
+        bulk_load(sm.sfb(s), sfb + ks * kSfBytes, kSfBytes, sm.full(s));
+      }
+      if (!ok) break;
+    }
+  } else if (warp == 1 && lane == 0) {
+    // ---------------------------------------------------------------- scale copies + UMMAs
+    constexpr uint32_t idesc = idesc_nvfp4(kTM, kTN);
+    uint32_t it = 0, nunit = 0;
+    bool ok = true;
+    NV41_FP4_FOR_EACH_UNIT(g, mt, nt, e) {
+      const uint32_t b = nunit & 1u, tph = (nunit >> 1) & 1u;
+      if (!mbar_wait(sm.tempty(b), tph ^ 1u, sm.abort_flag(), g.status, ST_TIMEOUT_TMEM_EMPTY)) break;
+      tc_fence_after_sync();
+      for (int ks = 0; ks < g.nstage; ++ks, ++it) {
+        const int s = it % kStages;
+        const uint32_t ph = (it / kStages) & 1u;
+        ok = mbar_wait(sm.full(s), ph, sm.abort_flag(), g.status, ST_TIMEOUT_FULL);
+        if (!ok) break;
+        tc_fence_after_sync();
+        const uint64_t adesc = umma_desc_kmajor_sw128(smem_u32(sm.a(s)));
+        const uint64_t bdesc = umma_desc_kmajor_sw128(smem_u32(sm.b(s)));
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          // scales of k-group j of this stage: one atom for A, one for B -> 4 TMEM columns each
+          sf_copy(tmem_base + kColSfa + 4 * j, sf_desc(smem_u32(sm.sfa(s) + 512 * j)));
+          sf_copy(tmem_base + kColSfb + 4 * j, sf_desc(smem_u32(sm.sfb(s) + 512 * j)));
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j)     // UMMA K = 64 e2m1 = 32 bytes = +2 in 16-byte units
+          umma_nvfp4(tmem_base + b * kTN, adesc + 2 * j, bdesc + 2 * j, idesc,
+                     tmem_base + kColSfa + 4 * j, tmem_base + kColSfb + 4 * j,
+                     (ks > 0 || j > 0) ? 1u : 0u);
+        umma_commit(sm.empty(s));
+      }
+      if (!ok) break;
+      umma_commit(sm.tfull(b));
+      ++nunit;
+    }
+  } else if (warp >= 4) {
+    // ---------------------------------------------------------------- epilogue (8 warps)
+    const int ew = warp - 4;
+    const int q = ew & 3, half = ew >> 2;
+    const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
+    uint32_t nunit = 0;
+    NV41_FP4_FOR_EACH_UNIT(g, mt, nt, e) {
+      const float sc = g.a_global * g.b_global[e];
+      const long long row = static_cast<long long>(mt) * kTM + q * 32 + lane;
+      const int n0 = nt * kTN + half * 64;
+      __nv_bfloat16* dst = g.out + row * g.ld_out + n0;
+      const uint32_t b = nunit & 1u, tph = (nunit >> 1) & 1u;
+      if (!mbar_wait<40>(sm.tfull(b), tph, sm.abort_flag(), g.status, ST_TIMEOUT_TMEM_FULL)) break;
+      tc_fence_after_sync();
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t v[16];
+        tmem_ld_32x32b_x16(lane_base + b * kTN + half * 64 + c * 16, v);
+        tmem_ld_wait_x16(v);
+#pragma unroll
+        for (int i = 0; i < 16; i += 8) {
+          if (n0 + c * 16 + i < g.N) {
+            uint32_t o[4];
+#pragma unroll
+            for (int p = 0; p < 4; ++p) {
+              const __nv_bfloat162 t = __floats2bfloat162_rn(__uint_as_float(v[i + 2 * p]) * sc,
+                                                             __uint_as_float(v[i + 2 * p + 1]) * sc);
+              o[p] = *reinterpret_cast<const uint32_t*>(&t);
+            }
+            *reinterpret_cast<uint4*>(dst + c * 16 + i) = make_uint4(o[0], o[1], o[2], o[3]);
+          }
+        }
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(sm.tempty(b));
+      ++nunit;
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  if (*sm.abort_flag()) {
+    for (int i = 0; i < 64; ++i) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) tmem_dealloc(tmem_base, 512);
+}
+
+}  // namespace fp4
+}  // namespace nv41
+
+using namespace nv41;
+
+extern "C" int nv41_moe_gemm_nvfp4(const void* a_packed, const void* a_sf, float a_global,
+                                   const void* b_packed, const void* b_sf, const float* b_global,
+                                   int E, int N, int Kpad, const int* tile_expert,
+                                   long long P_max, void* c_out, long long c_ld, unsigned* status,
+                                   void* stream) {
+  if (!a_packed || !a_sf || !b_packed || !b_sf || !b_global || !tile_expert || !c_out || !status)
+    return NV41_ERR_INVALID;
+  if (E <= 0 || N <= 0 || Kpad <= 0 || P_max <= 0 || (P_max % 128) != 0 || c_ld < N)
+    return NV41_ERR_INVALID;
+  if ((Kpad % 256) != 0 || (N % 128) != 0 || (c_ld % 8) != 0) return NV41_ERR_UNSUPPORTED;
+  fp4::Args g;
+  memset(&g, 0, sizeof(g));
+  int rc = make_tmap_2d(&g.tmap_a, a_packed, static_cast<unsigned long long>(P_max), Kpad / 2, 1,
+                        128, 128);
+  if (rc != NV41_OK) return rc;
+  rc = make_tmap_2d(&g.tmap_b, b_packed, static_cast<unsigned long long>(E) * N, Kpad / 2, 1, 128,
+                    128);
+  if (rc != NV41_OK) return rc;
+  g.sfa = static_cast<const uint8_t*>(a_sf);
+  g.sfb = static_cast<const uint8_t*>(b_sf);
+  g.tile_expert = tile_expert;
+  g.b_global = b_global;
+  g.a_global = a_global;
+  g.out = static_cast<__nv_bfloat16*>(c_out);
+  g.ld_out = c_ld;
+  g.N = N;
+  g.n_tiles_m = static_cast<int>(P_max / 128);
+  g.n_tiles_n = N / fp4::kTN;
+  g.nstage = Kpad / fp4::kStageK;
+  g.kgroups = Kpad / 64;
+  g.status = status;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(fp4::nvfp4_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             fp4::kSmemBytes) != cudaSuccess)
+      return NV41_ERR_CUDA;
+    configured = true;
+  }
+  const long long units = static_cast<long long>(g.n_tiles_m) * g.n_tiles_n;
+  int grid = sm_count();
+  if (units < grid) grid = static_cast<int>(units);
+  fp4::nvfp4_gemm_kernel<<<grid, fp4::kThreads, fp4::kSmemBytes,
+                           static_cast<cudaStream_t>(stream)>>>(g);
+  return launch_status();
+}

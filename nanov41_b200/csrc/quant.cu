@@ -236,6 +236,133 @@ quant_nvfp4_1x16_kernel(const void* __restrict__ xin, long long rows, int K, flo
   }
 }
 
+// ------------------------------------------------------------------------- NVFP4 for tcgen05
+// Same arithmetic as quant_nvfp4_1x16_kernel, laid out for the block-scaled tensor-core GEMM:
+// K padded to 256 (zero codes, zero scale bytes), rows optionally gathered (row index -1 = zero
+// row), and the e4m3 scale bytes written in 512-byte atoms
+//   sf[(row / 128) * (Kpad / 64) + k / 64][(row % 32) * 16 + (row / 32 % 4) * 4 + (k / 16) % 4].
+__device__ __forceinline__ long long sf_atom_offset(long long row, int blk16, int kgroups) {
+  return ((row >> 7) * kgroups + (blk16 >> 2)) * 512 + (row & 31) * 16 + ((row >> 5) & 3) * 4 +
+         (blk16 & 3);
+}
+
+__device__ __forceinline__ void nvfp4_block(const float (&f)[16], uint2& packed, uint8_t& sbyte) {
+  float amax = 0.f;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(f[i]));
+  amax = fmaxf(amax, 1e-8f);
+  const __nv_fp8_storage_t sb =
+      __nv_cvt_float_to_fp8(__fdiv_rn(amax, 6.0f), __NV_SATFINITE, __NV_E4M3);
+  const __half_raw hr = __nv_cvt_fp8_to_halfraw(sb, __NV_E4M3);
+  float s = __half2float(__half(hr));
+  s = fmaxf(s, 0.001953125f);
+  uint32_t words[2] = {0u, 0u};
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const uint32_t c = e2m1_code(__fdiv_rn(f[i], s));
+    words[i >> 3] |= c << (4 * (i & 7));
+  }
+  packed = make_uint2(words[0], words[1]);
+  sbyte = (s == 0.001953125f) ? static_cast<uint8_t>(0x01) : static_cast<uint8_t>(sb);
+}
+
+template <bool kInputFp32>
+__global__ void __launch_bounds__(256)
+quant_nvfp4_tc_kernel(const void* __restrict__ xin, long long ld_x, const int* __restrict__ gather,
+                      long long rows, int K, int Kpad, float global_scale,
+                      uint8_t* __restrict__ packed, uint8_t* __restrict__ sf) {
+  const int nblk = Kpad / 16, kgroups = Kpad / 64;
+  const long long n_items = rows * nblk;
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long item = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+       item < n_items; item += stride) {
+    const long long row = item / nblk;
+    const int blk = static_cast<int>(item - row * nblk);
+    const long long src = gather ? static_cast<long long>(gather[row]) : row;
+    uint2 out = make_uint2(0u, 0u);
+    uint8_t sb = 0;
+    if (blk * 16 < K) {
+      float f[16];
+#pragma unroll
+      for (int i = 0; i < 16; ++i) f[i] = 0.f;
+      if (src >= 0) {
+        if (kInputFp32) {
+          const float4* p = reinterpret_cast<const float4*>(
+              reinterpret_cast<const float*>(xin) + src * ld_x + blk * 16);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const float4 v = __ldg(p + i);
+            f[4 * i] = v.x; f[4 * i + 1] = v.y; f[4 * i + 2] = v.z; f[4 * i + 3] = v.w;
+          }
+        } else {
+          const uint4* p = reinterpret_cast<const uint4*>(
+              reinterpret_cast<const __nv_bfloat16*>(xin) + src * ld_x + blk * 16);
+          float lo[8], hi[8];
+          unpack_bf16x8(__ldg(p), lo);
+          unpack_bf16x8(__ldg(p + 1), hi);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) { f[i] = lo[i]; f[8 + i] = hi[i]; }
+        }
+        if (global_scale != 1.0f) {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) f[i] = __fdiv_rn(f[i], global_scale);
+        }
+      }
+      nvfp4_block(f, out, sb);
+    }
+    *reinterpret_cast<uint2*>(packed + row * (Kpad / 2) + blk * 8) = out;
+    sf[sf_atom_offset(row, blk, kgroups)] = sb;
+  }
+}
+
+// h = bf16(w * silu(min(g, L)) * clamp(u, +-L)) from bf16 gate|up rows [P, 2I], then NVFP4.
+__global__ void __launch_bounds__(256)
+swiglu_quant_nvfp4_kernel(const __nv_bfloat16* __restrict__ gu, const float* __restrict__ row_weight,
+                          const int* __restrict__ meta, int I, int Ipad, float L,
+                          float global_scale, uint8_t* __restrict__ packed,
+                          uint8_t* __restrict__ sf) {
+  const int nblk = Ipad / 16, kgroups = Ipad / 64;
+  const long long n_items = static_cast<long long>(meta[1]) * nblk;   // padded rows in use
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long item = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+       item < n_items; item += stride) {
+    const long long row = item / nblk;
+    const int blk = static_cast<int>(item - row * nblk);
+    uint2 out = make_uint2(0u, 0u);
+    uint8_t sb = 0;
+    if (blk * 16 < I) {
+      const float w = row_weight[row];
+      const uint4* pg = reinterpret_cast<const uint4*>(gu + row * 2 * I + blk * 16);
+      const uint4* pu = reinterpret_cast<const uint4*>(gu + row * 2 * I + I + blk * 16);
+      float g[16], u[16], f[16];
+      {
+        float lo[8], hi[8];
+        unpack_bf16x8(__ldg(pg), lo); unpack_bf16x8(__ldg(pg + 1), hi);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) { g[i] = lo[i]; g[8 + i] = hi[i]; }
+        unpack_bf16x8(__ldg(pu), lo); unpack_bf16x8(__ldg(pu + 1), hi);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) { u[i] = lo[i]; u[8 + i] = hi[i]; }
+      }
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        float gt = g[i], up = u[i];
+        if (L > 0.f) {
+          up = fminf(fmaxf(up, -L), L);
+          gt = fminf(gt, L);
+        }
+        const float sl = gt / (1.f + __expf(-gt));
+        float h = __bfloat162float(__float2bfloat16_rn((sl * up) * w));
+        if (global_scale != 1.0f) h = __fdiv_rn(h, global_scale);
+        f[i] = h;
+      }
+      nvfp4_block(f, out, sb);
+    }
+    *reinterpret_cast<uint2*>(packed + row * (Ipad / 2) + blk * 8) = out;
+    sf[sf_atom_offset(row, blk, kgroups)] = sb;
+  }
+}
+
 }  // namespace nv41
 
 using namespace nv41;
@@ -293,5 +420,45 @@ extern "C" int nv41_quant_nvfp4_1x16(const void* x, int x_is_fp32, long long row
                                      static_cast<cudaStream_t>(stream)>>>(
         x, rows, K, global_scale, static_cast<uint8_t*>(packed),
         static_cast<uint8_t*>(scale_bytes));
+  return launch_status();
+}
+
+extern "C" int nv41_quant_nvfp4_tc(const void* x, int x_is_fp32, long long ld_x,
+                                   const int* gather_rows, long long rows, int K,
+                                   float global_scale, void* packed, void* sf_atoms, void* stream) {
+  if (rows == 0) return NV41_OK;
+  if (!x || !packed || !sf_atoms || rows < 0 || K <= 0 || (K % 16) != 0 || ld_x < K ||
+      (ld_x % 8) != 0 || !(global_scale > 0.f))
+    return NV41_ERR_INVALID;
+  const int Kpad = (K + 255) / 256 * 256;
+  const long long items = rows * (Kpad / 16);
+  long long blocks = (items + 255) / 256;
+  if (blocks > 148LL * 64) blocks = 148LL * 64;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (x_is_fp32)
+    quant_nvfp4_tc_kernel<true><<<static_cast<unsigned>(blocks), 256, 0, st>>>(
+        x, ld_x, gather_rows, rows, K, Kpad, global_scale, static_cast<uint8_t*>(packed),
+        static_cast<uint8_t*>(sf_atoms));
+  else
+    quant_nvfp4_tc_kernel<false><<<static_cast<unsigned>(blocks), 256, 0, st>>>(
+        x, ld_x, gather_rows, rows, K, Kpad, global_scale, static_cast<uint8_t*>(packed),
+        static_cast<uint8_t*>(sf_atoms));
+  return launch_status();
+}
+
+extern "C" int nv41_swiglu_quant_nvfp4(const void* gu_bf16, const float* row_weight,
+                                       const int* meta, int I, long long P_max,
+                                       float swiglu_limit, float global_scale, void* packed,
+                                       void* sf_atoms, void* stream) {
+  if (!gu_bf16 || !row_weight || !meta || !packed || !sf_atoms || I <= 0 || (I % 16) != 0 ||
+      P_max <= 0 || !(global_scale > 0.f))
+    return NV41_ERR_INVALID;
+  const int Ipad = (I + 255) / 256 * 256;
+  long long blocks = (P_max * (Ipad / 16) + 255) / 256;
+  if (blocks > 148LL * 64) blocks = 148LL * 64;
+  swiglu_quant_nvfp4_kernel<<<static_cast<unsigned>(blocks), 256, 0,
+                              static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(gu_bf16), row_weight, meta, I, Ipad, swiglu_limit,
+      global_scale, static_cast<uint8_t*>(packed), static_cast<uint8_t*>(sf_atoms));
   return launch_status();
 }

@@ -362,3 +362,124 @@ def moe_forward_fp8(x: torch.Tensor, wq: Fp8ExpertWeights, weights: torch.Tensor
         return out, dict(layout=layout, x_codes=x_codes, x_scale=x_scale, h_codes=h_codes,
                          h_scale=h_scale, gate=gate, up=up, h=h, y_rows=y_rows)
     return out
+
+
+# --------------------------------------------------------------------------------- NVFP4 path
+def sf_atoms_to_rows(sf: torch.Tensor, rows: int, kpad: int) -> torch.Tensor:
+    """Undo the 512-byte atom order of the tensor-core scale layout: -> uint8 [rows, kpad/16]."""
+    kg = kpad // 64
+    nrb = sf.numel() // (kg * 512)
+    v = sf.view(nrb, kg, 32, 4, 4)                      # [row block, k group, r % 32, r / 32, j]
+    v = v.permute(0, 3, 2, 1, 4).reshape(nrb * 128, kg * 4)
+    return v[:rows].contiguous()
+
+
+def quant_nvfp4_tc(x: torch.Tensor, global_scale: float = 1.0, gather: torch.Tensor | None = None):
+    """bf16/fp32 [n, K] -> (packed e2m1 uint8 [rows, Kpad/2], scale atoms uint8) in the operand
+    layout of ``gemm_nvfp4`` (Kpad = K rounded up to 256; rows = len(gather) or n)."""
+    _need_cuda(x, gather)
+    if x.dtype not in (torch.bfloat16, torch.float32) or x.dim() != 2 or x.stride(1) != 1:
+        raise Nv41Error("quant_nvfp4_tc expects a 2-D bf16/fp32 tensor with unit inner stride")
+    K = x.shape[1]
+    rows = gather.numel() if gather is not None else x.shape[0]
+    kpad = ceil_to(K, 256)
+    packed = torch.empty((rows, kpad // 2), dtype=torch.uint8, device=x.device)
+    sf = torch.zeros(ceil_to(rows, 128) // 128 * (kpad // 64) * 512, dtype=torch.uint8,
+                     device=x.device)
+    check(_lib.load().nv41_quant_nvfp4_tc(_ptr(x), int(x.dtype == torch.float32), x.stride(0),
+                                          _ptr(gather), rows, K, float(global_scale), _ptr(packed),
+                                          _ptr(sf), _stream()), "nv41_quant_nvfp4_tc")
+    return packed, sf
+
+
+@dataclass
+class Nvfp4ExpertWeights:
+    """NVFP4 expert weights: packed e2m1 + e4m3 scale atoms + one fp32 global scale per tensor."""
+    w13_packed: torch.Tensor   # uint8 [E*2I, Dpad/2]
+    w13_sf: torch.Tensor
+    w13_global: torch.Tensor   # fp32 [E] (per-tensor value repeated)
+    w2_packed: torch.Tensor    # uint8 [E*D, Ipad/2]
+    w2_sf: torch.Tensor
+    w2_global: torch.Tensor
+    E: int
+    I: int
+    D: int
+
+
+def nvfp4_global_scale(w: torch.Tensor) -> float:
+    """Per-tensor scale amax / (448 * 6): block scales then use the full e4m3 range."""
+    return max(float(w.abs().amax().float()) / (448.0 * 6.0), 1e-30)
+
+
+def quantize_expert_weights_nvfp4(w1, w3, w2, g13: float | None = None,
+                                  g2: float | None = None) -> Nvfp4ExpertWeights:
+    """w1, w3: bf16 [E, I, D]; w2: bf16 [E, D, I].  One-off preparation (reads the tensor
+    maxima on the host unless the global scales are given)."""
+    E, I, D = w1.shape
+    w13 = torch.cat((w1, w3), dim=1).reshape(E * 2 * I, D).contiguous()
+    w2f = w2.reshape(E * D, I).contiguous()
+    g13 = nvfp4_global_scale(w13) if g13 is None else g13
+    g2 = nvfp4_global_scale(w2f) if g2 is None else g2
+    p13, s13 = quant_nvfp4_tc(w13, g13)
+    p2, s2 = quant_nvfp4_tc(w2f, g2)
+    dev = w1.device
+    return Nvfp4ExpertWeights(p13, s13, torch.full((E,), g13, dtype=torch.float32, device=dev),
+                              p2, s2, torch.full((E,), g2, dtype=torch.float32, device=dev),
+                              E, I, D)
+
+
+def gemm_nvfp4(a_packed, a_sf, a_global: float, b_packed, b_sf, b_global, E: int, N: int,
+               layout: DeviceLayout) -> torch.Tensor:
+    """Grouped C = (A @ B_e^T) * a_global * b_global[e] (bf16 [P_max, N]), block-scaled tcgen05."""
+    _need_cuda(a_packed, a_sf, b_packed, b_sf, b_global)
+    kpad = a_packed.shape[1] * 2
+    if b_packed.shape[1] * 2 != kpad or a_packed.shape[0] != layout.P_max:
+        raise Nv41Error("gemm_nvfp4: operand shapes do not match")
+    out = torch.empty((layout.P_max, N), dtype=torch.bfloat16, device=a_packed.device)
+    st = status_word(a_packed.device)
+    check(_lib.load().nv41_moe_gemm_nvfp4(_ptr(a_packed), _ptr(a_sf), float(a_global),
+                                          _ptr(b_packed), _ptr(b_sf), _ptr(b_global), E, N, kpad,
+                                          _ptr(layout.tile_expert), layout.P_max, _ptr(out),
+                                          out.stride(0), _ptr(st), _stream()),
+          "nv41_moe_gemm_nvfp4")
+    return out
+
+
+def swiglu_quant_nvfp4(gu: torch.Tensor, layout: DeviceLayout, limit: float,
+                       global_scale: float = 1.0):
+    """bf16 gate|up rows [P_max, 2I] -> NVFP4 h (packed [P_max, Ipad/2], scale atoms)."""
+    _need_cuda(gu)
+    P, twoI = gu.shape
+    I = twoI // 2
+    ipad = ceil_to(I, 256)
+    packed = torch.zeros((P, ipad // 2), dtype=torch.uint8, device=gu.device)
+    sf = torch.zeros(P // 128 * (ipad // 64) * 512, dtype=torch.uint8, device=gu.device)
+    check(_lib.load().nv41_swiglu_quant_nvfp4(_ptr(gu), _ptr(layout.row_weight), _ptr(layout.meta),
+                                              I, P, float(limit), float(global_scale),
+                                              _ptr(packed), _ptr(sf), _stream()),
+          "nv41_swiglu_quant_nvfp4")
+    return packed, sf
+
+
+def moe_forward_nvfp4(x, wq: Nvfp4ExpertWeights, weights, indices, limit: float,
+                      shared: torch.Tensor | None = None, x_global: float = 1.0,
+                      h_global: float = 1.0, layout: DeviceLayout | None = None,
+                      return_parts: bool = False):
+    """Routed-experts forward with NVFP4 weights AND NVFP4 activations (W4A4, as the reference's
+    nvfp4_gemm quantises both operands): gather+quantise x rows, gate/up GEMM, SwiGLU + NVFP4
+    re-quantisation of h, down GEMM, fp32 top-k combine (+ shared)."""
+    _need_cuda(x, weights, indices)
+    T, D = x.shape
+    k = indices.shape[1]
+    if layout is None:
+        layout = build_layout(indices.reshape(-1), wq.E, k, weights.reshape(-1))
+    xp, xsf = quant_nvfp4_tc(x.contiguous(), x_global, gather=layout.row_token)
+    gu = gemm_nvfp4(xp, xsf, x_global, wq.w13_packed, wq.w13_sf, wq.w13_global, wq.E, 2 * wq.I,
+                    layout)
+    hp, hsf = swiglu_quant_nvfp4(gu, layout, limit, h_global)
+    y_rows = gemm_nvfp4(hp, hsf, h_global, wq.w2_packed, wq.w2_sf, wq.w2_global, wq.E, wq.D, layout)
+    out = combine(y_rows, layout.row_of_flat, T, k, shared)
+    if return_parts:
+        return out, dict(layout=layout, x_packed=xp, x_sf=xsf, gu=gu, h_packed=hp, h_sf=hsf,
+                         y_rows=y_rows)
+    return out

@@ -202,3 +202,44 @@ def moe_fp8_backward(x, dout, weights, indices, limit, prepared, parts):
     dws_flat = torch.empty(R)
     dws_flat.index_copy_(0, order, dws_rows)
     return dict(dx=dx, dws=dws_flat.view(T, k), dw1=dw1, dw3=dw3, dw2=dw2)
+
+
+def moe_nvfp4(x, w1, w3, w2, weights, indices, limit, g13, g2, x_global=1.0, h_global=1.0,
+              shared=None, return_parts=False):
+    """Dequantise-then-fp32-matmul oracle of the W4A4 NVFP4 expert path: both operands of both
+    GEMMs go through quantize_nvfp4 (experiments/tl_kernels/nvfp4_gemm.py:229-241 quantises a and
+    b alike), outputs are rounded to bf16 at the reference's rounding points."""
+    T, k = indices.shape
+    E, I, D = w1.shape
+    w13 = torch.cat((w1, w3), dim=1)
+    w13d = Q.nvfp4_dequant(*Q.nvfp4_quant(w13.reshape(E * 2 * I, D), g13), g13).view(E, 2 * I, D)
+    w2d = Q.nvfp4_dequant(*Q.nvfp4_quant(w2.reshape(E * D, I), g2), g2).view(E, D, I)
+    xp, xs = Q.nvfp4_quant(x, x_global)
+    xd = Q.nvfp4_dequant(xp, xs, x_global)
+    order, tok, counts = sort_tokens(indices, E)
+    ws = weights.reshape(-1).index_select(0, order)
+    R = T * k
+    gu_all = torch.zeros(R, 2 * I, dtype=torch.bfloat16)
+    h_all = torch.zeros(R, I, dtype=torch.bfloat16)
+    outs = torch.zeros(R, D, dtype=torch.bfloat16)
+    pos = 0
+    for e in range(E):
+        c = int(counts[e])
+        if c:
+            sl = slice(pos, pos + c)
+            gu = (xd[tok[sl]] @ w13d[e].t()).to(torch.bfloat16)
+            h = swiglu(gu[:, :I].float(), gu[:, I:].float(), limit, ws[sl, None]).to(torch.bfloat16)
+            hd = Q.nvfp4_dequant(*Q.nvfp4_quant(h, h_global), h_global)
+            outs[sl] = (hd @ w2d[e].t()).to(torch.bfloat16)
+            gu_all[sl], h_all[sl] = gu, h
+        pos += c
+    flat = torch.empty(R, D, dtype=torch.float32)
+    flat.index_copy_(0, order, outs.float())
+    y = flat.view(T, k, D).sum(1)
+    if shared is not None:
+        y = y + shared
+    y = y.to(torch.bfloat16)
+    if return_parts:
+        return y, dict(order=order, tok=tok, counts=counts, gu=gu_all, h=h_all, outs=outs,
+                       x_packed=xp, x_scale=xs)
+    return y
