@@ -45,10 +45,13 @@ int nv41_status_read(const unsigned* status, unsigned* raw_host, void* stream);
  * x: bf16 [*, ld_x]; output row r reads source row gather_rows[r] (or r when NULL; -1 = zeros).
  * codes: u8 [rows, Kpad], Kpad = ceil(K/128)*128.  scales[r*stride_row + kb*stride_kb] fp32.
  * K % 8 == 0.  (The reference asserts K % 128 == 0; a short last block is quantised as if
- * zero-padded, which leaves amax, scale and the real codes unchanged.) */
+ * zero-padded, which leaves amax, scale and the real codes unchanged.)  ue8m0 != 0 selects the
+ * reference's scale_fmt = "ue8m0" (ref/kernel.py:22-37,77-78; the model default,
+ * nanov41/_ref_patched_model.py:42): the scale rounded up to a power of two, still stored as fp32. */
 int nv41_quant_fp8_1x128(const void* x_bf16, long long ld_x, const int* gather_rows,
                          long long rows, int K, void* codes, float* scales,
-                         long long scale_stride_row, long long scale_stride_kb, void* stream);
+                         long long scale_stride_row, long long scale_stride_kb, int ue8m0,
+                         void* stream);
 
 /* FP8-e4m3 128x128 weight quantizer.  The reference has no 128x128 quantizer (weights arrive
  * pre-quantised; layout consumed by ref/kernel.py:232,259-264, dequantised by
@@ -57,7 +60,7 @@ int nv41_quant_fp8_1x128(const void* x_bf16, long long ld_x, const int* gather_r
  * w: bf16 [E, N, K] contiguous.  codes: u8 [E*N, Kpad].  scales: fp32 [E, ceil(N/128), Kpad/128].
  * codes_t (optional): transposed copy u8 [E*Kpad, Npad], Npad = ceil(N/128)*128, zero padded. */
 int nv41_quant_fp8_128x128(const void* w_bf16, int E, int N, int K, void* codes, void* codes_t,
-                           float* scales, void* stream);
+                           float* scales, int ue8m0, void* stream);
 
 /* NVFP4-e2m1 1x16 quantizer; experiments/tl_kernels/nvfp4_gemm.py:97-126 (quantize_nvfp4)
  * applied to x / global_scale (global_scale = 1 reproduces the reference, which has no
@@ -145,6 +148,39 @@ int nv41_moe_gemm_fp8(int a_mode, const void* a_src, long long a_ld, const float
                       int E, int N, int K, const int* tile_expert, const int* row_token,
                       long long P_max, void* c_out, long long c_ld, unsigned* status,
                       void* stream);
+
+/* ---- FP8 with power-of-two (ue8m0) scales applied by the tensor core ----------------------- */
+
+/* fp32 power-of-two scales (as the quantizers write them in ue8m0 mode) -> e8m0 bytes in the
+ * 512-byte atoms the block-scaled UMMA reads: atoms[row/128][kb][(r%32)*16 + (r/32)*4 + j], the
+ * byte replicated over j = 0..3.  rows form: scales_kmajor[kb*kb_stride + row]; blocks form: one
+ * scale per 128x128 weight block, n_blocks = E * ceil(N/128) * (K/128), same order as the
+ * quantizer's scale tensor.  (The reference keeps e8m0 scales per row / per block,
+ * ref/kernel.py:232,259-264; this is their tensor-core layout.) */
+int nv41_sf_pack_ue8m0_rows(const float* scales_kmajor, long long kb_stride, long long rows,
+                            int nkb, void* atoms, void* stream);
+int nv41_sf_pack_ue8m0_blocks(const float* block_scales, long long n_blocks, void* atoms,
+                              void* stream);
+
+/* nv41_moe_gemm1_fp8 / nv41_moe_gemm_fp8 for scale_fmt = "ue8m0" (ref/kernel.py:22-37,77-78; the
+ * model default nanov41/_ref_patched_model.py:42): tcgen05 kind::mxf8f6f4.block_scale, scales
+ * applied by the tensor core, accumulator resident in TMEM over the whole K loop.
+ * Gathered A (a_mode 1): a_src = codes [T, a_ld], a_scale_kmajor = fp32 powers of two [K/128][T];
+ * contiguous A (a_mode 0): a_src = codes [P_max, K], a_sf = scale atoms.  Weight scale atoms from
+ * nv41_sf_pack_ue8m0_blocks.  gemm1 writes h codes [P_max, I], h_scale fp32 [I/128][P_max] and
+ * h_sf atoms [P_max/128][I/128][512].  K % 128 == 0, I % 128 == 0, N % 128 == 0. */
+int nv41_moe_gemm1_mx(int a_mode, const void* a_src, long long a_ld, const float* a_scale_kmajor,
+                      long long a_scale_kb_stride, const void* a_sf, long long a_rows,
+                      const void* w13_codes, const void* w13_sf, int E, int I, int K,
+                      const int* tile_expert, const int* row_token, const float* row_weight,
+                      long long P_max, float swiglu_limit, void* h_codes, float* h_scale,
+                      void* h_sf, void* gate_out, void* up_out, void* h_out, unsigned* status,
+                      void* stream);
+int nv41_moe_gemm_mx(int a_mode, const void* a_src, long long a_ld, const float* a_scale_kmajor,
+                     long long a_scale_kb_stride, const void* a_sf, long long a_rows,
+                     const void* b_codes, const void* b_sf, int E, int N, int K,
+                     const int* tile_expert, const int* row_token, long long P_max, void* c_out,
+                     long long c_ld, unsigned* status, void* stream);
 
 /* ---- NVFP4 (block-scaled tcgen05) --------------------------------------------------------- */
 

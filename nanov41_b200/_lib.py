@@ -20,8 +20,8 @@ _p, _i, _ll, _f = C.c_void_p, C.c_int, C.c_longlong, C.c_float
 SIGNATURES = {
     "nv41_abi_version": (_i, []),
     "nv41_status_read": (_i, [_p, _p, _p]),
-    "nv41_quant_fp8_1x128": (_i, [_p, _ll, _p, _ll, _i, _p, _p, _ll, _ll, _p]),
-    "nv41_quant_fp8_128x128": (_i, [_p, _i, _i, _i, _p, _p, _p, _p]),
+    "nv41_quant_fp8_1x128": (_i, [_p, _ll, _p, _ll, _i, _p, _p, _ll, _ll, _i, _p]),
+    "nv41_quant_fp8_128x128": (_i, [_p, _i, _i, _i, _p, _p, _p, _i, _p]),
     "nv41_quant_nvfp4_1x16": (_i, [_p, _i, _ll, _i, _f, _p, _p, _p]),
     "nv41_moe_layout_workspace_bytes": (_ll, [_ll, _i]),
     "nv41_moe_layout_build": (_i, [_p, _i, _p, _ll, _i, _i, _ll, _p, _p, _p, _p, _p, _p, _p,
@@ -34,6 +34,12 @@ SIGNATURES = {
                                 _ll, _f, _p, _p, _p, _p, _p, _p, _p]),
     "nv41_moe_gemm_fp8": (_i, [_i, _p, _ll, _p, _ll, _ll, _p, _p, _ll, _ll, _ll, _i, _i, _i,
                                _p, _p, _ll, _p, _ll, _p, _p]),
+    "nv41_sf_pack_ue8m0_rows": (_i, [_p, _ll, _ll, _i, _p, _p]),
+    "nv41_sf_pack_ue8m0_blocks": (_i, [_p, _ll, _p, _p]),
+    "nv41_moe_gemm1_mx": (_i, [_i, _p, _ll, _p, _ll, _p, _ll, _p, _p, _i, _i, _i, _p, _p, _p, _ll,
+                               _f, _p, _p, _p, _p, _p, _p, _p, _p]),
+    "nv41_moe_gemm_mx": (_i, [_i, _p, _ll, _p, _ll, _p, _ll, _p, _p, _i, _i, _i, _p, _p, _ll, _p,
+                              _ll, _p, _p]),
     "nv41_quant_nvfp4_tc": (_i, [_p, _i, _ll, _p, _ll, _i, _f, _p, _p, _p]),
     "nv41_swiglu_quant_nvfp4": (_i, [_p, _p, _p, _i, _ll, _f, _f, _p, _p, _p]),
     "nv41_moe_gemm_nvfp4": (_i, [_p, _p, _f, _p, _p, _p, _i, _i, _i, _p, _ll, _p, _ll, _p, _p]),

@@ -1,0 +1,613 @@
+// Grouped FP8 expert GEMMs with power-of-two (ue8m0) block scales applied by the tensor core:
+// tcgen05 kind::mxf8f6f4.block_scale, TMA-fed, the accumulator resident in TMEM for the whole K
+// loop.  This is the reference's scale_fmt = "ue8m0" mode (ref/kernel.py:22-37,77-78 round_scale;
+// the model default, nanov41/_ref_patched_model.py:42-43): with power-of-two scales nothing has
+// to be promoted per K block, so the per-128-K TMEM round trip of the fp32-scale kernel
+// (gemm_fp8.cu) disappears.  Same maths otherwise: ref/kernel.py:207-274 (fp8_gemm), the
+// gate/up + SwiGLU + re-quantised h fusion of nanov41/triton_grouped_moe.py:947-1043 and the
+// plain grouped GEMM of :1046-1093.
+//
+// Scales reach the tensor core as e8m0 bytes in TMEM.  A 1x128 activation scale (or a 128x128
+// weight scale) is one byte replicated over the four 32-wide K sub-blocks the hardware scales
+// separately; 128 rows x 4 bytes form the 512-byte atom
+//   atom[(r % 32) * 16 + (r / 32) * 4 + j]   (j = 32-wide sub-block; CUTLASS
+//   Sm1xxBlockScaledBasicChunk order) that one tcgen05.cp (32x128b.warpx4) moves into 4 TMEM columns.
+//
+// CTA (512 threads): warp 0 TMA producer (weights, their scale atoms; contiguous activations and
+// their atoms), warp 1 scale copies + UMMAs (+ TMEM allocation), warps 2-3 gathered-activation
+// producers (rows by token with cp.async, scale atom built in shared memory), warps 8-15
+// epilogue.  Tile 128 x 256, stage = 128 of K.  TMEM: one 256-column accumulator + 12 scale
+// columns; the epilogue copies the accumulator to registers, releases TMEM at once, and does
+// SwiGLU / re-quantisation / stores while the next tile's UMMAs run.  All waits are bounded.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp8.h>
+#include <cstdint>
+#include <cstring>
+
+#include "../../include/nanov41_b200.h"
+#include "ptx.cuh"
+#include "tmap.cuh"
+#include "util.cuh"
+
+namespace nv41 {
+namespace mx {
+
+constexpr int kBM = 128, kBN = 256, kBK = 128;
+constexpr int kABytes = kBM * kBK, kBBytes = kBN * kBK;
+constexpr int kSfaOff = kABytes + kBBytes;            // 512-byte A atom, then two B atoms
+constexpr int kStageBytes = kABytes + kBBytes + 2048; // keeps every stage 1024-byte aligned
+constexpr int kStages = 4;
+constexpr int kThreads = 512;
+constexpr uint32_t kColSfa = 256, kColSfb = 260;
+constexpr int kSmemBytes =
+    kStages * kStageBytes + (2 * kStages + 4) * 8 + 16 + 2 * 64 * 4 + 2 * 2 * 128 * 4 + 1024;
+
+enum { A_TMA = 0, A_GATHER = 1 };
+enum { EPI_SWIGLU = 0, EPI_STORE = 1 };
+
+struct Args {
+  CUtensorMap tmap_a, tmap_b;
+  const uint8_t* a_codes;        // gather: [T, a_ld]
+  long long a_ld;
+  const float* a_scale;          // gather: fp32 powers of two, [K/128][T]
+  long long a_scale_kb_stride;
+  const uint8_t* a_sf;           // contiguous A: atoms [P_max/128][K/128][512]
+  const uint8_t* b_sf;           // atoms [E * b_rows_per_expert / 128][K/128][512]
+  const int* tile_expert;
+  const int* row_token;
+  const float* row_weight;
+  int n_tiles_m, n_tiles_n, nkb;
+  int b_rows_per_expert, b_up_row_offset, N;
+  float limit;
+  uint8_t* h_codes;              // SwiGLU: [P_max, N]
+  float* h_scale;                // [N/128][P_max] fp32 (powers of two)
+  uint8_t* h_sf;                 // atoms [P_max/128][N/128][512]
+  __nv_bfloat16 *gate_out, *up_out, *h_out;
+  __nv_bfloat16* c_out;          // store: [P_max, c_ld]
+  long long c_ld, P_max;
+  uint32_t* status;
+};
+
+struct Smem {
+  uint8_t* base;
+  __device__ uint8_t* a(int s) const { return base + s * kStageBytes; }
+  __device__ uint8_t* b(int s) const { return base + s * kStageBytes + kABytes; }
+  __device__ uint8_t* sfa(int s) const { return base + s * kStageBytes + kSfaOff; }
+  __device__ uint8_t* sfb(int s) const { return sfa(s) + 512; }
+  __device__ uint64_t* bars() const { return reinterpret_cast<uint64_t*>(base + kStages * kStageBytes); }
+  __device__ uint64_t* full(int s) const { return bars() + s; }
+  __device__ uint64_t* empty(int s) const { return bars() + kStages + s; }
+  __device__ uint64_t* tfull() const { return bars() + 2 * kStages; }
+  __device__ uint64_t* tempty() const { return bars() + 2 * kStages + 1; }
+  __device__ uint64_t* xbar(int b) const { return bars() + 2 * kStages + 2 + b; }
+  __device__ uint32_t* tmem_slot() const { return reinterpret_cast<uint32_t*>(bars() + 2 * kStages + 4); }
+  __device__ volatile uint32_t* abort_flag() const { return tmem_slot() + 1; }
+  __device__ int* gather_tok() const { return reinterpret_cast<int*>(tmem_slot() + 4); }      // [2][64]
+  __device__ float* xch() const { return reinterpret_cast<float*>(gather_tok() + 128); }      // [2][2][128]
+};
+
+__device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+      :
+      : "r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar))
+      : "memory");
+}
+__device__ __forceinline__ uint64_t sf_desc(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_addr >> 4) & 0x3FFFu);
+  d |= static_cast<uint64_t>(128 >> 4) << 32;
+  d |= static_cast<uint64_t>(1) << 46;
+  return d;
+}
+__device__ __forceinline__ void sf_copy(uint32_t taddr, uint64_t desc) {
+  asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(desc) : "memory");
+}
+// kind::mxf8f6f4 descriptor: e4m3 x e4m3, ue8m0 scales, K-major, scale byte `sf` of the TMEM word
+__host__ __device__ constexpr uint32_t idesc_mx(int M, int N, int sf) {
+  return (static_cast<uint32_t>(sf) << 4) | (static_cast<uint32_t>(N >> 3) << 17) | (1u << 23) |
+         (static_cast<uint32_t>(M >> 4) << 24) | (static_cast<uint32_t>(sf) << 29);
+}
+__device__ __forceinline__ void umma_mx(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc,
+                                        uint32_t idesc, uint32_t tsfa, uint32_t tsfb,
+                                        uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %6, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%4], [%5], p;\n\t}"
+      :
+      : "r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(tsfa), "r"(tsfb), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src, uint32_t src_bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes)
+               : "memory");
+}
+__device__ __forceinline__ uint32_t pack_bf16x2(float a, float b) {
+  const __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
+__device__ __forceinline__ float bf16_round(float x) {
+  return __bfloat162float(__float2bfloat16_rn(x));
+}
+
+#define NV41_MX_FOR_EACH_UNIT(g, mt, nt, e)                                                       \
+  for (int w_ = blockIdx.x, total_ = (g).n_tiles_m * (g).n_tiles_n, mt = 0, nt = 0, e = 0;        \
+       w_ < total_; w_ += gridDim.x)                                                              \
+    if ((mt = w_ / (g).n_tiles_n, nt = w_ - mt * (g).n_tiles_n, e = (g).tile_expert[mt]) >= 0)
+
+// ------------------------------------------------------------------------------ TMA warp
+template <int MODE_A, int EPI>
+__device__ __forceinline__ void role_tma(const Args& g, const Smem& sm) {
+  uint32_t it = 0;
+  const int rb_per_expert = g.b_rows_per_expert / 128;
+  NV41_MX_FOR_EACH_UNIT(g, mt, nt, e) {
+    int brow0, brow1, rb0, rb1;
+    if (EPI == EPI_SWIGLU) {
+      brow0 = e * g.b_rows_per_expert + nt * 128;
+      brow1 = brow0 + g.b_up_row_offset;
+      rb0 = e * rb_per_expert + nt;
+      rb1 = rb0 + g.b_up_row_offset / 128;
+    } else {
+      brow0 = e * g.b_rows_per_expert + nt * kBN;
+      brow1 = brow0 + 128;
+      rb0 = e * rb_per_expert + nt * 2;
+      rb1 = min(rb0 + 1, (e + 1) * rb_per_expert - 1);   // a half tile past N is masked anyway
+    }
+    const uint8_t* sfb0 = g.b_sf + static_cast<long long>(rb0) * g.nkb * 512;
+    const uint8_t* sfb1 = g.b_sf + static_cast<long long>(rb1) * g.nkb * 512;
+    const uint8_t* sfa = (MODE_A == A_TMA) ? g.a_sf + static_cast<long long>(mt) * g.nkb * 512 : nullptr;
+    for (int kb = 0; kb < g.nkb; ++kb, ++it) {
+      const int s = it % kStages;
+      const uint32_t ph = (it / kStages) & 1u;
+      if (!mbar_wait(sm.empty(s), ph ^ 1u, sm.abort_flag(), g.status, ST_TIMEOUT_EMPTY)) return;
+      const uint32_t bytes = kBBytes + 1024 + (MODE_A == A_TMA ? kABytes + 512 : 0);
+      mbar_arrive_expect_tx(sm.full(s), bytes);
+      if (MODE_A == A_TMA) {
+        tma_load_2d(sm.a(s), &g.tmap_a, kb * kBK, mt * kBM, sm.full(s));
+        bulk_load(sm.sfa(s), sfa + kb * 512, 512, sm.full(s));
+      }
+      tma_load_2d(sm.b(s), &g.tmap_b, kb * kBK, brow0, sm.full(s));
+      tma_load_2d(sm.b(s) + 128 * kBK, &g.tmap_b, kb * kBK, brow1, sm.full(s));
+      bulk_load(sm.sfb(s), sfb0 + kb * 512, 512, sm.full(s));
+      bulk_load(sm.sfb(s) + 512, sfb1 + kb * 512, 512, sm.full(s));
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------ UMMA warp
+__device__ __forceinline__ void role_mma(const Args& g, const Smem& sm, uint32_t tmem_base) {
+  uint32_t it = 0, unit = 0;
+  const uint32_t tsfa = tmem_base + kColSfa, tsfb = tmem_base + kColSfb;
+  NV41_MX_FOR_EACH_UNIT(g, mt, nt, e) {
+    // the single accumulator must have been copied out by the epilogue of the previous tile
+    if (!mbar_wait(sm.tempty(), (unit & 1u) ^ 1u, sm.abort_flag(), g.status, ST_TIMEOUT_TMEM_EMPTY))
+      return;
+    tc_fence_after_sync();
+    for (int kb = 0; kb < g.nkb; ++kb, ++it) {
+      const int s = it % kStages;
+      const uint32_t ph = (it / kStages) & 1u;
+      if (!mbar_wait(sm.full(s), ph, sm.abort_flag(), g.status, ST_TIMEOUT_FULL)) return;
+      tc_fence_after_sync();
+      sf_copy(tsfa, sf_desc(smem_u32(sm.sfa(s))));
+      sf_copy(tsfb, sf_desc(smem_u32(sm.sfb(s))));
+      sf_copy(tsfb + 4, sf_desc(smem_u32(sm.sfb(s) + 512)));
+      const uint64_t adesc = umma_desc_kmajor_sw128(smem_u32(sm.a(s)));
+      const uint64_t bdesc = umma_desc_kmajor_sw128(smem_u32(sm.b(s)));
+      umma_mx(tmem_base, adesc, bdesc, idesc_mx(kBM, kBN, 0), tsfa, tsfb, kb > 0 ? 1u : 0u);
+      umma_mx(tmem_base, adesc + 2, bdesc + 2, idesc_mx(kBM, kBN, 1), tsfa, tsfb, 1u);
+      umma_mx(tmem_base, adesc + 4, bdesc + 4, idesc_mx(kBM, kBN, 2), tsfa, tsfb, 1u);
+      umma_mx(tmem_base, adesc + 6, bdesc + 6, idesc_mx(kBM, kBN, 3), tsfa, tsfb, 1u);
+      umma_commit(sm.empty(s));
+    }
+    umma_commit(sm.tfull());
+    ++unit;
+  }
+}
+
+// ------------------------------------------------------------------------------ A producers
+// 2 warps x 64 rows.  Codes: lane -> 16-byte chunk (lane & 7) of rows (lane >> 3) + 4 i, by
+// cp.async with zero fill for padding rows; scale atom: lane -> rows lane, lane + 32 of the
+// warp's 64, the token's e8m0 exponent byte replicated over the four K sub-blocks.
+__device__ __forceinline__ void role_gather(const Args& g, const Smem& sm, int gw, int lane) {
+  uint32_t it = 0;
+  const int c = lane & 7, rsub = lane >> 3;
+  int* tokbuf = sm.gather_tok() + gw * 64;
+  int pending = -1;
+  NV41_MX_FOR_EACH_UNIT(g, mt, nt, e) {
+    __syncwarp();
+    tokbuf[lane] = g.row_token[mt * kBM + gw * 64 + lane];
+    tokbuf[lane + 32] = g.row_token[mt * kBM + gw * 64 + 32 + lane];
+    __syncwarp();
+    for (int kb = 0; kb < g.nkb; ++kb, ++it) {
+      const int s = it % kStages;
+      const uint32_t ph = (it / kStages) & 1u;
+      if (!mbar_wait<40>(sm.empty(s), ph ^ 1u, sm.abort_flag(), g.status, ST_TIMEOUT_EMPTY)) return;
+      const uint32_t dst = smem_u32(sm.a(s));
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        const int rl = i * 4 + rsub;
+        const int r = gw * 64 + rl;
+        const int tok = tokbuf[rl];
+        const uint8_t* src = g.a_codes + (tok >= 0 ? tok : 0) * g.a_ld + kb * kBK + c * 16;
+        cp_async_16(dst + r * 128 + ((c ^ (r & 7)) << 4), src, tok >= 0 ? 16u : 0u);
+      }
+      asm volatile("cp.async.commit_group;" ::: "memory");
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int rl = lane + 32 * h, r = gw * 64 + rl;
+        const int tok = tokbuf[rl];
+        uint32_t byte = 127u;                               // 2^0 for padding rows (codes are zero)
+        if (tok >= 0)
+          byte = (__float_as_uint(__ldg(g.a_scale + kb * g.a_scale_kb_stride + tok)) >> 23) & 0xFFu;
+        *reinterpret_cast<uint32_t*>(sm.sfa(s) + (r & 31) * 16 + (r >> 5) * 4) = byte * 0x01010101u;
+      }
+      if (pending >= 0) {
+        asm volatile("cp.async.wait_group 1;" ::: "memory");
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(sm.full(pending));
+      }
+      pending = s;
+    }
+  }
+  if (pending >= 0) {
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    fence_proxy_async_smem();
+    __syncwarp();
+    if (lane == 0) mbar_arrive(sm.full(pending));
+  }
+}
+
+// ------------------------------------------------------------------------------ epilogue
+// 8 warps; thread = (row = TMEM lane, column half).  The 128 accumulators of the thread are
+// copied out of TMEM first and the accumulator is released, so the UMMAs of the next tile start
+// while SwiGLU / quantisation / stores run from registers.
+template <int EPI>
+__device__ __forceinline__ void role_epilogue(const Args& g, const Smem& sm, uint32_t tmem_base,
+                                              int ew, int lane) {
+  const int q = ew & 3, half = ew >> 2;
+  const int row_in_tile = q * 32 + lane;
+  const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
+  uint32_t unit = 0;
+  NV41_MX_FOR_EACH_UNIT(g, mt, nt, e) {
+    const long long grow = static_cast<long long>(mt) * kBM + row_in_tile;
+    if (!mbar_wait<40>(sm.tfull(), unit & 1u, sm.abort_flag(), g.status, ST_TIMEOUT_TMEM_FULL)) return;
+    tc_fence_after_sync();
+    float acc[128];
+    // piece c: SwiGLU -> gate columns half*64 + 16c (c < 4), up columns 128 + half*64 + 16(c-4);
+    // store -> columns half*128 + 16c
+#pragma unroll
+    for (int c = 0; c < 8; c += 2) {
+      uint32_t va[16], vb[16];
+      const uint32_t c0 = (EPI == EPI_SWIGLU) ? ((c >> 2) * 128 + half * 64 + (c & 3) * 16)
+                                              : (half * 128 + c * 16);
+      tmem_ld_32x32b_x16(lane_base + c0, va);
+      tmem_ld_32x32b_x16(lane_base + c0 + 16, vb);
+      tmem_ld_wait_x16(va);
+      tmem_ld_wait_x16(vb);
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        acc[c * 16 + i] = __uint_as_float(va[i]);
+        acc[(c + 1) * 16 + i] = __uint_as_float(vb[i]);
+      }
+    }
+    tc_fence_before_sync();
+    __syncwarp();
+    if (lane == 0) mbar_arrive(sm.tempty());
+
+    if (EPI == EPI_SWIGLU) {
+      const float wr = g.row_weight[grow];
+      const float L = g.limit;
+      const long long ocol = static_cast<long long>(nt) * 128 + half * 64;
+      if (g.gate_out) {
+#pragma unroll
+        for (int i = 0; i < 64; i += 8) {
+          uint4 vg, vu;
+          vg.x = pack_bf16x2(acc[i], acc[i + 1]);     vg.y = pack_bf16x2(acc[i + 2], acc[i + 3]);
+          vg.z = pack_bf16x2(acc[i + 4], acc[i + 5]); vg.w = pack_bf16x2(acc[i + 6], acc[i + 7]);
+          vu.x = pack_bf16x2(acc[64 + i], acc[65 + i]); vu.y = pack_bf16x2(acc[66 + i], acc[67 + i]);
+          vu.z = pack_bf16x2(acc[68 + i], acc[69 + i]); vu.w = pack_bf16x2(acc[70 + i], acc[71 + i]);
+          *reinterpret_cast<uint4*>(g.gate_out + grow * g.N + ocol + i) = vg;
+          *reinterpret_cast<uint4*>(g.up_out + grow * g.N + ocol + i) = vu;
+        }
+      }
+      float amax = 0.f;
+#pragma unroll
+      for (int i = 0; i < 64; ++i) {
+        float gt = bf16_round(acc[i]);            // Linear output is bf16, then .float()
+        float up = bf16_round(acc[64 + i]);
+        if (L > 0.f) {
+          up = fminf(fmaxf(up, -L), L);
+          gt = fminf(gt, L);
+        }
+        const float hg = 0.5f * gt;               // silu(g) = g/2 * (1 + tanh(g/2))
+        const float sl = fmaf(hg, tanh_approx(hg), hg);
+        const float hv = bf16_round((sl * up) * wr);
+        acc[i] = hv;
+        amax = fmaxf(amax, fabsf(hv));
+      }
+      if (g.h_out) {
+#pragma unroll
+        for (int i = 0; i < 64; i += 8) {
+          uint4 vh;
+          vh.x = pack_bf16x2(acc[i], acc[i + 1]);     vh.y = pack_bf16x2(acc[i + 2], acc[i + 3]);
+          vh.z = pack_bf16x2(acc[i + 4], acc[i + 5]); vh.w = pack_bf16x2(acc[i + 6], acc[i + 7]);
+          *reinterpret_cast<uint4*>(g.h_out + grow * g.N + ocol + i) = vh;
+        }
+      }
+      // the 1x128 block of h spans both column halves: exchange the partial maxima
+      float* x = sm.xch() + (unit & 1u) * 256;
+      x[half * 128 + row_in_tile] = amax;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(sm.xbar(unit & 1u));
+      if (!mbar_wait<40>(sm.xbar(unit & 1u), (unit >> 1) & 1u, sm.abort_flag(), g.status,
+                         ST_TIMEOUT_AUX))
+        return;
+      amax = fmaxf(x[row_in_tile], x[128 + row_in_tile]);
+      // ue8m0 scale: max(amax, 1e-4) / 448 rounded up to a power of two; h / s is then exact
+      float s = fmaxf(amax, 1e-4f) * (1.0f / 448.0f);
+      uint32_t sb = __float_as_uint(s);
+      uint32_t ebits = (sb >> 23) & 0xFFu;
+      if (sb & 0x7FFFFFu) ++ebits;
+      s = __uint_as_float(ebits << 23);
+      const float rinv = __uint_as_float((254u - ebits) << 23);      // 2^-e, exact
+      uint8_t* hp = g.h_codes + grow * g.N + ocol;
+#pragma unroll
+      for (int i = 0; i < 64; i += 16) {
+        uint32_t wds[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const uint32_t lo = __nv_cvt_float2_to_fp8x2(
+              make_float2(acc[i + 4 * j] * rinv, acc[i + 4 * j + 1] * rinv), __NV_SATFINITE, __NV_E4M3);
+          const uint32_t hi = __nv_cvt_float2_to_fp8x2(
+              make_float2(acc[i + 4 * j + 2] * rinv, acc[i + 4 * j + 3] * rinv), __NV_SATFINITE, __NV_E4M3);
+          wds[j] = lo | (hi << 16);
+        }
+        *reinterpret_cast<uint4*>(hp + i) = make_uint4(wds[0], wds[1], wds[2], wds[3]);
+      }
+      if (half == 0) {
+        g.h_scale[static_cast<long long>(nt) * g.P_max + grow] = s;
+        const long long atom = (static_cast<long long>(mt) * (g.N / 128) + nt) * 512;
+        *reinterpret_cast<uint32_t*>(g.h_sf + atom + (row_in_tile & 31) * 16 + (row_in_tile >> 5) * 4) =
+            ebits * 0x01010101u;
+      }
+    } else {
+      const long long ocol = static_cast<long long>(nt) * kBN + half * 128;
+      __nv_bfloat16* cp = g.c_out + grow * g.c_ld + ocol;
+#pragma unroll
+      for (int i = 0; i < 128; i += 8) {
+        if (ocol + i < g.N) {
+          uint4 vc;
+          vc.x = pack_bf16x2(acc[i], acc[i + 1]);     vc.y = pack_bf16x2(acc[i + 2], acc[i + 3]);
+          vc.z = pack_bf16x2(acc[i + 4], acc[i + 5]); vc.w = pack_bf16x2(acc[i + 6], acc[i + 7]);
+          *reinterpret_cast<uint4*>(cp + i) = vc;
+        }
+      }
+    }
+    ++unit;
+  }
+}
+
+// ------------------------------------------------------------------------------ kernel
+template <int MODE_A, int EPI>
+__global__ void __launch_bounds__(kThreads, 1) gemm_mx_kernel(const __grid_constant__ Args g) {
+  extern __shared__ uint8_t smem_raw[];
+  Smem sm;
+  sm.base = reinterpret_cast<uint8_t*>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(sm.full(s), MODE_A == A_TMA ? 1u : 3u);
+      mbar_init(sm.empty(s), 1u);
+    }
+    mbar_init(sm.tfull(), 1u);
+    mbar_init(sm.tempty(), 8u);
+    mbar_init(sm.xbar(0), 8u);
+    mbar_init(sm.xbar(1), 8u);
+    *sm.abort_flag() = 0u;
+    fence_mbar_init();
+    tma_prefetch_desc(&g.tmap_b);
+    if (MODE_A == A_TMA) tma_prefetch_desc(&g.tmap_a);
+  }
+  if (warp == 1) {
+    tmem_alloc(sm.tmem_slot(), 512);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *sm.tmem_slot();
+
+  const int wg = warp >> 2;
+  if (wg == 0) {
+    setmaxnreg_dec<64>();
+    if (warp == 0) {
+      if (lane == 0) role_tma<MODE_A, EPI>(g, sm);
+    } else if (warp == 1) {
+      if (lane == 0) role_mma(g, sm, tmem_base);
+    } else if (MODE_A == A_GATHER) {
+      role_gather(g, sm, warp - 2, lane);
+    }
+  } else if (wg == 1) {
+    setmaxnreg_dec<24>();
+  } else {
+    setmaxnreg_inc<208>();
+    role_epilogue<EPI>(g, sm, tmem_base, warp - 8, lane);
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  if (*sm.abort_flag()) {
+    for (int i = 0; i < 64; ++i) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) tmem_dealloc(tmem_base, 512);
+}
+
+// ------------------------------------------------------------------------------ scale atoms
+// fp32 power-of-two scales -> e8m0 bytes in 512-byte atoms.
+// rows mode : scales[kb * kb_stride + row]            -> atoms[row / 128][kb]
+// block mode: scales[(e * nnb + nb) * nkb + kb] (one per 128x128 block) -> atoms[e * nnb + nb][kb]
+__global__ void __launch_bounds__(256)
+sf_pack_rows_kernel(const float* __restrict__ scales, long long kb_stride, long long rows, int nkb,
+                    uint8_t* __restrict__ atoms) {
+  const long long n = rows * nkb;
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
+    const long long row = i % rows;
+    const int kb = static_cast<int>(i / rows);
+    const uint32_t byte = (__float_as_uint(scales[kb * kb_stride + row]) >> 23) & 0xFFu;
+    const int r = static_cast<int>(row & 127);
+    *reinterpret_cast<uint32_t*>(atoms + ((row >> 7) * nkb + kb) * 512 + (r & 31) * 16 + (r >> 5) * 4) =
+        byte * 0x01010101u;
+  }
+}
+__global__ void __launch_bounds__(128)
+sf_pack_blocks_kernel(const float* __restrict__ scales, long long n_blocks, uint8_t* __restrict__ atoms) {
+  const long long blk = blockIdx.x;
+  if (blk >= n_blocks) return;
+  const uint32_t byte = (__float_as_uint(scales[blk]) >> 23) & 0xFFu;
+  reinterpret_cast<uint32_t*>(atoms + blk * 512)[threadIdx.x] = byte * 0x01010101u;
+}
+
+template <int MODE_A, int EPI>
+static int launch(const Args& a, cudaStream_t st) {
+  static bool configured = false;
+  auto kern = gemm_mx_kernel<MODE_A, EPI>;
+  if (!configured) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess)
+      return NV41_ERR_CUDA;
+    configured = true;
+  }
+  const long long units = static_cast<long long>(a.n_tiles_m) * a.n_tiles_n;
+  if (units <= 0) return NV41_OK;
+  int grid = sm_count();
+  if (units < grid) grid = static_cast<int>(units);
+  kern<<<grid, kThreads, kSmemBytes, st>>>(a);
+  return launch_status();
+}
+
+}  // namespace mx
+}  // namespace nv41
+
+using namespace nv41;
+
+extern "C" int nv41_sf_pack_ue8m0_rows(const float* scales_kmajor, long long kb_stride,
+                                       long long rows, int nkb, void* atoms, void* stream) {
+  if (rows == 0) return NV41_OK;
+  if (!scales_kmajor || !atoms || rows < 0 || nkb <= 0 || kb_stride < rows) return NV41_ERR_INVALID;
+  long long blocks = (rows * nkb + 255) / 256;
+  if (blocks > 148LL * 16) blocks = 148LL * 16;
+  mx::sf_pack_rows_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      scales_kmajor, kb_stride, rows, nkb, static_cast<uint8_t*>(atoms));
+  return launch_status();
+}
+
+extern "C" int nv41_sf_pack_ue8m0_blocks(const float* block_scales, long long n_blocks, void* atoms,
+                                         void* stream) {
+  if (n_blocks == 0) return NV41_OK;
+  if (!block_scales || !atoms || n_blocks < 0) return NV41_ERR_INVALID;
+  mx::sf_pack_blocks_kernel<<<static_cast<unsigned>(n_blocks), 128, 0,
+                              static_cast<cudaStream_t>(stream)>>>(block_scales, n_blocks,
+                                                                   static_cast<uint8_t*>(atoms));
+  return launch_status();
+}
+
+extern "C" int nv41_moe_gemm1_mx(int a_mode, const void* a_src, long long a_ld,
+                                 const float* a_scale_kmajor, long long a_scale_kb_stride,
+                                 const void* a_sf, long long a_rows, const void* w13_codes,
+                                 const void* w13_sf, int E, int I, int K, const int* tile_expert,
+                                 const int* row_token, const float* row_weight, long long P_max,
+                                 float swiglu_limit, void* h_codes, float* h_scale, void* h_sf,
+                                 void* gate_out, void* up_out, void* h_out, unsigned* status,
+                                 void* stream) {
+  if (!a_src || !w13_codes || !w13_sf || !tile_expert || !row_token || !row_weight || !h_codes ||
+      !h_scale || !h_sf || !status)
+    return NV41_ERR_INVALID;
+  if (E <= 0 || I <= 0 || K <= 0 || P_max <= 0 || (P_max % 128) != 0) return NV41_ERR_INVALID;
+  if ((K % 128) != 0 || (I % 128) != 0) return NV41_ERR_UNSUPPORTED;
+  if ((gate_out == nullptr) != (up_out == nullptr)) return NV41_ERR_INVALID;
+  if (a_mode == mx::A_GATHER ? !a_scale_kmajor : !a_sf) return NV41_ERR_INVALID;
+  if (a_mode != mx::A_TMA && a_mode != mx::A_GATHER) return NV41_ERR_UNSUPPORTED;
+  mx::Args g;
+  memset(&g, 0, sizeof(g));
+  int rc = make_tmap_2d(&g.tmap_b, w13_codes, static_cast<unsigned long long>(E) * 2 * I, K, 1, 128, 128);
+  if (rc != NV41_OK) return rc;
+  if (a_mode == mx::A_TMA) {
+    rc = make_tmap_2d(&g.tmap_a, a_src, static_cast<unsigned long long>(a_rows), K, 1, 128, 128);
+    if (rc != NV41_OK) return rc;
+  }
+  g.a_codes = static_cast<const uint8_t*>(a_src);
+  g.a_ld = a_ld;
+  g.a_scale = a_scale_kmajor;
+  g.a_scale_kb_stride = a_scale_kb_stride;
+  g.a_sf = static_cast<const uint8_t*>(a_sf);
+  g.b_sf = static_cast<const uint8_t*>(w13_sf);
+  g.tile_expert = tile_expert;
+  g.row_token = row_token;
+  g.row_weight = row_weight;
+  g.n_tiles_m = static_cast<int>(P_max / 128);
+  g.n_tiles_n = I / 128;
+  g.nkb = K / 128;
+  g.b_rows_per_expert = 2 * I;
+  g.b_up_row_offset = I;
+  g.N = I;
+  g.limit = swiglu_limit;
+  g.h_codes = static_cast<uint8_t*>(h_codes);
+  g.h_scale = h_scale;
+  g.h_sf = static_cast<uint8_t*>(h_sf);
+  g.gate_out = static_cast<__nv_bfloat16*>(gate_out);
+  g.up_out = static_cast<__nv_bfloat16*>(up_out);
+  g.h_out = static_cast<__nv_bfloat16*>(h_out);
+  g.P_max = P_max;
+  g.status = status;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (a_mode == mx::A_TMA) return mx::launch<mx::A_TMA, mx::EPI_SWIGLU>(g, st);
+  return mx::launch<mx::A_GATHER, mx::EPI_SWIGLU>(g, st);
+}
+
+extern "C" int nv41_moe_gemm_mx(int a_mode, const void* a_src, long long a_ld,
+                                const float* a_scale_kmajor, long long a_scale_kb_stride,
+                                const void* a_sf, long long a_rows, const void* b_codes,
+                                const void* b_sf, int E, int N, int K, const int* tile_expert,
+                                const int* row_token, long long P_max, void* c_out, long long c_ld,
+                                unsigned* status, void* stream) {
+  if (!a_src || !b_codes || !b_sf || !tile_expert || !c_out || !status) return NV41_ERR_INVALID;
+  if (E <= 0 || N <= 0 || K <= 0 || P_max <= 0 || (P_max % 128) != 0 || c_ld < N)
+    return NV41_ERR_INVALID;
+  if ((K % 128) != 0 || (N % 128) != 0 || (c_ld % 8) != 0) return NV41_ERR_UNSUPPORTED;
+  if (a_mode == mx::A_GATHER ? (!a_scale_kmajor || !row_token) : !a_sf) return NV41_ERR_INVALID;
+  if (a_mode != mx::A_TMA && a_mode != mx::A_GATHER) return NV41_ERR_UNSUPPORTED;
+  mx::Args g;
+  memset(&g, 0, sizeof(g));
+  int rc = make_tmap_2d(&g.tmap_b, b_codes, static_cast<unsigned long long>(E) * N, K, 1, 128, 128);
+  if (rc != NV41_OK) return rc;
+  if (a_mode == mx::A_TMA) {
+    rc = make_tmap_2d(&g.tmap_a, a_src, static_cast<unsigned long long>(a_rows), K, 1, 128, 128);
+    if (rc != NV41_OK) return rc;
+  }
+  g.a_codes = static_cast<const uint8_t*>(a_src);
+  g.a_ld = a_ld;
+  g.a_scale = a_scale_kmajor;
+  g.a_scale_kb_stride = a_scale_kb_stride;
+  g.a_sf = static_cast<const uint8_t*>(a_sf);
+  g.b_sf = static_cast<const uint8_t*>(b_sf);
+  g.tile_expert = tile_expert;
+  g.row_token = row_token;
+  g.n_tiles_m = static_cast<int>(P_max / 128);
+  g.n_tiles_n = (N + mx::kBN - 1) / mx::kBN;
+  g.nkb = K / 128;
+  g.b_rows_per_expert = N;
+  g.N = N;
+  g.c_out = static_cast<__nv_bfloat16*>(c_out);
+  g.c_ld = c_ld;
+  g.P_max = P_max;
+  g.status = status;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (a_mode == mx::A_TMA) return mx::launch<mx::A_TMA, mx::EPI_STORE>(g, st);
+  return mx::launch<mx::A_GATHER, mx::EPI_STORE>(g, st);
+}

@@ -29,6 +29,21 @@ __device__ __forceinline__ void unpack_bf16x8(const uint4& v, float (&f)[8]) {
   }
 }
 
+// Block scale from the block maximum.  fp32 mode: max(amax, 1e-4) * fl32(1/448)
+// (ref/kernel.py:76,80).  ue8m0 mode (the reference's scale_fmt = "ue8m0"): that value rounded
+// up to a power of two, 2^ceil(log2(.)), by the exponent-bit arithmetic of
+// ref/kernel.py:22-37 (fast_log2_ceil / fast_pow2, fast_round_scale).
+__device__ __forceinline__ float block_scale(float amax, int ue8m0) {
+  float s = fmaxf(amax, 1e-4f) * (1.0f / 448.0f);
+  if (ue8m0) {
+    const uint32_t b = __float_as_uint(s);
+    uint32_t e = (b >> 23) & 0xFFu;
+    if (b & 0x7FFFFFu) ++e;
+    s = __uint_as_float(e << 23);
+  }
+  return s;
+}
+
 // e4m3 code of clamp(x / s, +-448), round-to-nearest-even, saturating.
 __device__ __forceinline__ uint32_t fp8x4_codes(float a, float b, float c, float d, float s) {
   float q0 = fminf(fmaxf(__fdiv_rn(a, s), -448.f), 448.f);
@@ -47,7 +62,7 @@ __global__ void __launch_bounds__(256)
 quant_fp8_1x128_kernel(const __nv_bfloat16* __restrict__ x, long long ld_x,
                        const int* __restrict__ gather, uint8_t* __restrict__ codes,
                        float* __restrict__ scales, long long ss_row, long long ss_kb,
-                       long long rows, int K, int Kpad) {
+                       long long rows, int K, int Kpad, int ue8m0) {
   const int nkb = Kpad / 128;
   const long long n_items = rows * nkb;
   const int lane = threadIdx.x & 31;
@@ -55,8 +70,6 @@ quant_fp8_1x128_kernel(const __nv_bfloat16* __restrict__ x, long long ld_x,
   const long long half_id =
       (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 4;
   const long long n_halves = (static_cast<long long>(gridDim.x) * blockDim.x) >> 4;
-  const float inv448 = 1.0f / 448.0f;   // fl32(1/448), folded at compile time
-
   const unsigned hmask = 0xFFFFu << (lane & 16);   // shuffles stay inside the half-warp
   for (long long item = half_id; item < n_items; item += n_halves) {
     const long long row = item / nkb;
@@ -77,8 +90,7 @@ quant_fp8_1x128_kernel(const __nv_bfloat16* __restrict__ x, long long ld_x,
     for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(f[i]));
 #pragma unroll
     for (int o = 8; o >= 1; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(hmask, amax, o));
-    amax = fmaxf(amax, 1e-4f);
-    const float s = amax * inv448;
+    const float s = block_scale(amax, ue8m0);
     uint2 out;
     out.x = fp8x4_codes(f[0], f[1], f[2], f[3], s);
     out.y = fp8x4_codes(f[4], f[5], f[6], f[7], s);
@@ -95,7 +107,7 @@ quant_fp8_1x128_kernel(const __nv_bfloat16* __restrict__ x, long long ld_x,
 __global__ void __launch_bounds__(256)
 quant_fp8_128x128_kernel(const __nv_bfloat16* __restrict__ w, int E, int N, int K, int Kpad,
                          int Npad, uint8_t* __restrict__ codes, uint8_t* __restrict__ codes_t,
-                         float* __restrict__ scales) {
+                         float* __restrict__ scales, int ue8m0) {
   __shared__ float red[8];
   __shared__ float s_scale;
   __shared__ __align__(16) uint8_t tile[128][128 + 16];
@@ -128,8 +140,7 @@ quant_fp8_128x128_kernel(const __nv_bfloat16* __restrict__ w, int E, int N, int 
     float m = red[0];
 #pragma unroll
     for (int i = 1; i < 8; ++i) m = fmaxf(m, red[i]);
-    m = fmaxf(m, 1e-4f);
-    const float s = m * (1.0f / 448.0f);
+    const float s = block_scale(m, ue8m0);
     s_scale = s;
     scales[(static_cast<long long>(e) * nnb + nb) * nkb + kb] = s;
   }
@@ -370,7 +381,7 @@ using namespace nv41;
 extern "C" int nv41_quant_fp8_1x128(const void* x_bf16, long long ld_x, const int* gather_rows,
                                     long long rows, int K, void* codes, float* scales,
                                     long long scale_stride_row, long long scale_stride_kb,
-                                    void* stream) {
+                                    int ue8m0, void* stream) {
   if (rows == 0) return NV41_OK;
   if (!x_bf16 || !codes || !scales || rows < 0 || K <= 0 || (K % 8) != 0 || ld_x < K)
     return NV41_ERR_INVALID;
@@ -382,12 +393,13 @@ extern "C" int nv41_quant_fp8_1x128(const void* x_bf16, long long ld_x, const in
   quant_fp8_1x128_kernel<<<static_cast<unsigned>(blocks), 256, 0,
                            static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(x_bf16), ld_x, gather_rows,
-      static_cast<uint8_t*>(codes), scales, scale_stride_row, scale_stride_kb, rows, K, Kpad);
+      static_cast<uint8_t*>(codes), scales, scale_stride_row, scale_stride_kb, rows, K, Kpad,
+      ue8m0);
   return launch_status();
 }
 
 extern "C" int nv41_quant_fp8_128x128(const void* w_bf16, int E, int N, int K, void* codes,
-                                      void* codes_t, float* scales, void* stream) {
+                                      void* codes_t, float* scales, int ue8m0, void* stream) {
   if (!w_bf16 || !codes || !scales || E <= 0 || N <= 0 || K <= 0 || (K % 8) != 0)
     return NV41_ERR_INVALID;
   const int Kpad = (K + 127) / 128 * 128;
@@ -395,7 +407,7 @@ extern "C" int nv41_quant_fp8_128x128(const void* w_bf16, int E, int N, int K, v
   dim3 grid(Kpad / 128, (N + 127) / 128, E);
   quant_fp8_128x128_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(w_bf16), E, N, K, Kpad, Npad,
-      static_cast<uint8_t*>(codes), static_cast<uint8_t*>(codes_t), scales);
+      static_cast<uint8_t*>(codes), static_cast<uint8_t*>(codes_t), scales, ue8m0);
   return launch_status();
 }
 

@@ -64,7 +64,7 @@ def check_status(device=None) -> None:
 
 # --------------------------------------------------------------------------------- quantizers
 def quant_fp8_1x128(x: torch.Tensor, gather: torch.Tensor | None = None, rows: int | None = None,
-                    scale_kmajor: bool = False):
+                    scale_kmajor: bool = False, ue8m0: bool = False):
     """bf16 [n, K] -> (e4m3 codes as uint8 [rows, Kpad], fp32 scales).
 
     Scales are [rows, Kpad/128] (the reference's layout) or, with ``scale_kmajor``,
@@ -84,12 +84,12 @@ def quant_fp8_1x128(x: torch.Tensor, gather: torch.Tensor | None = None, rows: i
         scales = torch.empty((n_rows, kpad // 128), dtype=torch.float32, device=x.device)
         ss_row, ss_kb = kpad // 128, 1
     check(_lib.load().nv41_quant_fp8_1x128(_ptr(x), x.stride(0), _ptr(gather), n_rows, K,
-                                           _ptr(codes), _ptr(scales), ss_row, ss_kb, _stream()),
-          "nv41_quant_fp8_1x128")
+                                           _ptr(codes), _ptr(scales), ss_row, ss_kb, int(ue8m0),
+                                           _stream()), "nv41_quant_fp8_1x128")
     return codes, scales
 
 
-def quant_fp8_128x128(w: torch.Tensor, transposed: bool = False):
+def quant_fp8_128x128(w: torch.Tensor, transposed: bool = False, ue8m0: bool = False):
     """bf16 [E, N, K] -> (codes uint8 [E, N, Kpad], scales fp32 [E, ceil(N/128), Kpad/128]
     [, codes_t uint8 [E, Kpad, Npad]])."""
     _need_cuda(w)
@@ -101,7 +101,8 @@ def quant_fp8_128x128(w: torch.Tensor, transposed: bool = False):
     scales = torch.empty((E, npad // 128, kpad // 128), dtype=torch.float32, device=w.device)
     codes_t = torch.empty((E, kpad, npad), dtype=torch.uint8, device=w.device) if transposed else None
     check(_lib.load().nv41_quant_fp8_128x128(_ptr(w), E, N, K, _ptr(codes), _ptr(codes_t),
-                                             _ptr(scales), _stream()), "nv41_quant_fp8_128x128")
+                                             _ptr(scales), int(ue8m0), _stream()),
+          "nv41_quant_fp8_128x128")
     return (codes, scales, codes_t) if transposed else (codes, scales)
 
 
@@ -261,6 +262,47 @@ def gemm_fp8(a_mode: int, a_codes: torch.Tensor, a_scale_kmajor: torch.Tensor,
     return out
 
 
+def gemm1_mx(a_mode: int, a_codes, a_scale_kmajor, a_sf, w13_codes, w13_sf, layout: DeviceLayout,
+             limit: float, save_gate_up: bool = False, save_h: bool = False):
+    """ue8m0 counterpart of ``gemm1_fp8`` (scales applied by the tensor core).  Returns
+    (h_codes, h_scale fp32 [I/128, P_max], h_sf atoms, gate, up, h)."""
+    _need_cuda(a_codes, w13_codes, w13_sf)
+    E, twoI, K = w13_codes.shape
+    I = twoI // 2
+    P = layout.P_max
+    dev = a_codes.device
+    h_codes = torch.empty((P, I), dtype=torch.uint8, device=dev)
+    h_scale = torch.empty((I // 128, P), dtype=torch.float32, device=dev)
+    h_sf = torch.zeros(P // 128 * (I // 128) * 512, dtype=torch.uint8, device=dev)
+    gate = torch.empty((P, I), dtype=torch.bfloat16, device=dev) if save_gate_up else None
+    up = torch.empty((P, I), dtype=torch.bfloat16, device=dev) if save_gate_up else None
+    h = torch.empty((P, I), dtype=torch.bfloat16, device=dev) if save_h else None
+    st = status_word(dev)
+    check(_lib.load().nv41_moe_gemm1_mx(
+        a_mode, _ptr(a_codes), a_codes.stride(0), _ptr(a_scale_kmajor),
+        0 if a_scale_kmajor is None else a_scale_kmajor.stride(0), _ptr(a_sf), a_codes.shape[0],
+        _ptr(w13_codes), _ptr(w13_sf), E, I, K, _ptr(layout.tile_expert), _ptr(layout.row_token),
+        _ptr(layout.row_weight), P, float(limit), _ptr(h_codes), _ptr(h_scale), _ptr(h_sf),
+        _ptr(gate), _ptr(up), _ptr(h), _ptr(st), _stream()), "nv41_moe_gemm1_mx")
+    return h_codes, h_scale, h_sf, gate, up, h
+
+
+def gemm_mx(a_mode: int, a_codes, a_scale_kmajor, a_sf, b_codes, b_sf,
+            layout: DeviceLayout) -> torch.Tensor:
+    """ue8m0 counterpart of ``gemm_fp8``: grouped C = A @ B_e^T, bf16 [P_max, N]."""
+    _need_cuda(a_codes, b_codes, b_sf)
+    E, N, K = b_codes.shape
+    P = layout.P_max
+    out = torch.empty((P, N), dtype=torch.bfloat16, device=a_codes.device)
+    st = status_word(a_codes.device)
+    check(_lib.load().nv41_moe_gemm_mx(
+        a_mode, _ptr(a_codes), a_codes.stride(0), _ptr(a_scale_kmajor),
+        0 if a_scale_kmajor is None else a_scale_kmajor.stride(0), _ptr(a_sf), a_codes.shape[0],
+        _ptr(b_codes), _ptr(b_sf), E, N, K, _ptr(layout.tile_expert), _ptr(layout.row_token), P,
+        _ptr(out), out.stride(0), _ptr(st), _stream()), "nv41_moe_gemm_mx")
+    return out
+
+
 # --------------------------------------------------------------------------------- layer
 @dataclass
 class Fp8ExpertWeights:
@@ -274,18 +316,51 @@ class Fp8ExpertWeights:
     D: int
     w13_codes_t: torch.Tensor | None = None   # uint8 [E, Dpad, 2I]  (backward: dX GEMM)
     w2_codes_t: torch.Tensor | None = None    # uint8 [E, Ipad, Dpad] (backward: dact GEMM)
+    ue8m0: bool = False                       # power-of-two scales (scale_fmt = "ue8m0")
+    w13_sf: torch.Tensor | None = None        # ue8m0: e8m0 scale atoms for the tensor core
+    w2_sf: torch.Tensor | None = None
+    w13_sf_t: torch.Tensor | None = None      # atoms of the transposed copies
+    w2_sf_t: torch.Tensor | None = None
+
+
+def pack_sf_rows(scales_kmajor: torch.Tensor) -> torch.Tensor:
+    """fp32 power-of-two scales [K/128, rows] -> e8m0 scale atoms for the block-scaled GEMM."""
+    nkb, rows = scales_kmajor.shape
+    atoms = torch.zeros(ceil_to(rows, 128) // 128 * nkb * 512, dtype=torch.uint8,
+                        device=scales_kmajor.device)
+    check(_lib.load().nv41_sf_pack_ue8m0_rows(_ptr(scales_kmajor), scales_kmajor.stride(0), rows,
+                                              nkb, _ptr(atoms), _stream()),
+          "nv41_sf_pack_ue8m0_rows")
+    return atoms
+
+
+def pack_sf_blocks(block_scales: torch.Tensor) -> torch.Tensor:
+    """fp32 power-of-two 128x128 block scales [E, N/128, K/128] -> e8m0 scale atoms."""
+    sc = block_scales.contiguous()
+    atoms = torch.empty(sc.numel() * 512, dtype=torch.uint8, device=sc.device)
+    check(_lib.load().nv41_sf_pack_ue8m0_blocks(_ptr(sc), sc.numel(), _ptr(atoms), _stream()),
+          "nv41_sf_pack_ue8m0_blocks")
+    return atoms
 
 
 def quantize_expert_weights(w1: torch.Tensor, w3: torch.Tensor, w2: torch.Tensor,
-                            transposed: bool = False) -> Fp8ExpertWeights:
+                            transposed: bool = False, ue8m0: bool = False) -> Fp8ExpertWeights:
     """w1, w3: bf16 [E, I, D]; w2: bf16 [E, D, I] (the [out, in] orientation Linear stores).
-    ``transposed`` also produces the transposed code copies the backward GEMMs read."""
+    ``transposed`` also produces the transposed code copies the backward GEMMs read; ``ue8m0``
+    selects power-of-two scales (the reference's scale_fmt = "ue8m0") and the tensor-core scale
+    atoms that go with them."""
     E, I, D = w1.shape
     w13 = torch.cat((w1, w3), dim=1).contiguous()
-    r13 = quant_fp8_128x128(w13, transposed)
-    r2 = quant_fp8_128x128(w2.contiguous(), transposed)
-    return Fp8ExpertWeights(r13[0], r13[1], r2[0], r2[1], E, I, D,
-                            r13[2] if transposed else None, r2[2] if transposed else None)
+    r13 = quant_fp8_128x128(w13, transposed, ue8m0)
+    r2 = quant_fp8_128x128(w2.contiguous(), transposed, ue8m0)
+    wq = Fp8ExpertWeights(r13[0], r13[1], r2[0], r2[1], E, I, D,
+                          r13[2] if transposed else None, r2[2] if transposed else None, ue8m0)
+    if ue8m0:
+        wq.w13_sf, wq.w2_sf = pack_sf_blocks(r13[1]), pack_sf_blocks(r2[1])
+        if transposed:
+            wq.w13_sf_t = pack_sf_blocks(r13[1].transpose(1, 2))
+            wq.w2_sf_t = pack_sf_blocks(r2[1].transpose(1, 2))
+    return wq
 
 
 def gather_rows(src: torch.Tensor, rows: torch.Tensor) -> torch.Tensor:
@@ -352,11 +427,17 @@ def moe_forward_fp8(x: torch.Tensor, wq: Fp8ExpertWeights, weights: torch.Tensor
     k = indices.shape[1]
     if layout is None:
         layout = build_layout(indices.reshape(-1), wq.E, k, weights.reshape(-1))
-    x_codes, x_scale = quant_fp8_1x128(x.contiguous(), scale_kmajor=True)
-    h_codes, h_scale, gate, up, h = gemm1_fp8(A_GATHER_FP8, x_codes, x_scale, wq.w13_codes,
-                                              wq.w13_scale, layout, limit,
-                                              save_gate_up=return_parts, save_h=return_parts)
-    y_rows = gemm_fp8(A_CONTIGUOUS, h_codes, h_scale, wq.w2_codes, wq.w2_scale, layout)
+    x_codes, x_scale = quant_fp8_1x128(x.contiguous(), scale_kmajor=True, ue8m0=wq.ue8m0)
+    if wq.ue8m0:
+        h_codes, h_scale, h_sf, gate, up, h = gemm1_mx(
+            A_GATHER_FP8, x_codes, x_scale, None, wq.w13_codes, wq.w13_sf, layout, limit,
+            save_gate_up=return_parts, save_h=return_parts)
+        y_rows = gemm_mx(A_CONTIGUOUS, h_codes, None, h_sf, wq.w2_codes, wq.w2_sf, layout)
+    else:
+        h_codes, h_scale, gate, up, h = gemm1_fp8(A_GATHER_FP8, x_codes, x_scale, wq.w13_codes,
+                                                  wq.w13_scale, layout, limit,
+                                                  save_gate_up=return_parts, save_h=return_parts)
+        y_rows = gemm_fp8(A_CONTIGUOUS, h_codes, h_scale, wq.w2_codes, wq.w2_scale, layout)
     out = combine(y_rows, layout.row_of_flat, T, k, shared)
     if return_parts:
         return out, dict(layout=layout, x_codes=x_codes, x_scale=x_scale, h_codes=h_codes,

@@ -58,27 +58,27 @@ def moe_bf16(x, w1, w3, w2, weights, indices, limit, shared=None):
     return y.to(x.dtype)
 
 
-def quantize_weights_fp8(w1, w3, w2):
+def quantize_weights_fp8(w1, w3, w2, ue8m0=False):
     """W13 = cat(w1, w3) per expert along the output dim (nanov41/fast_moe.py:371,385), then
     128x128 block quantisation of W13 [E,2I,D] and W2 [E,D,I]."""
     w13 = torch.cat((w1, w3), dim=1)
-    c13, s13 = Q.fp8_quant_128x128(w13)
-    c2, s2 = Q.fp8_quant_128x128(w2)
+    c13, s13 = Q.fp8_quant_128x128(w13, ue8m0)
+    c2, s2 = Q.fp8_quant_128x128(w2, ue8m0)
     return (c13, s13), (c2, s2)
 
 
-def prepare_weights_fp8(w1, w3, w2):
+def prepare_weights_fp8(w1, w3, w2, ue8m0=False):
     """Quantise the expert weights 128x128 and return them dequantised to fp32
     (w13d [E, 2I, D], w2d [E, D, I]) together with the codes/scales."""
     E, I, D = w1.shape
-    (c13, s13), (c2, s2) = quantize_weights_fp8(w1, w3, w2)
+    (c13, s13), (c2, s2) = quantize_weights_fp8(w1, w3, w2, ue8m0)
     w13d = Q.fp8_dequant_128x128(c13, s13)[:, :, :D].contiguous()
     w2d = Q.fp8_dequant_128x128(c2, s2)[:, :, :I].contiguous()
-    return dict(w13d=w13d, w2d=w2d, w13=(c13, s13), w2=(c2, s2), E=E, I=I, D=D)
+    return dict(w13d=w13d, w2d=w2d, w13=(c13, s13), w2=(c2, s2), E=E, I=I, D=D, ue8m0=ue8m0)
 
 
 def moe_fp8(x, w1, w3, w2, weights, indices, limit, shared=None, return_parts=False,
-            prepared=None):
+            prepared=None, ue8m0=False):
     """Dequantise-then-fp32-matmul oracle of the FP8 expert path (forward).
 
     x -> act_quant 1x128 (per token row) -> dequant -> @ dequant(W13)^T in fp32 -> bf16
@@ -88,11 +88,12 @@ def moe_fp8(x, w1, w3, w2, weights, indices, limit, shared=None, return_parts=Fa
     ``prepared`` = prepare_weights_fp8(...) skips the weight quantisation (w1/w3/w2 unused)."""
     T, k = indices.shape
     if prepared is None:
-        prepared = prepare_weights_fp8(w1, w3, w2)
+        prepared = prepare_weights_fp8(w1, w3, w2, ue8m0)
+    ue8m0 = prepared.get("ue8m0", ue8m0)      # scale_fmt of the whole path
     E, I, D = prepared["E"], prepared["I"], prepared["D"]
     w13d, w2d = prepared["w13d"], prepared["w2d"]
     (c13, s13), (c2, s2) = prepared["w13"], prepared["w2"]
-    xc, xsc = Q.fp8_quant_1x128(x)
+    xc, xsc = Q.fp8_quant_1x128(x, ue8m0)
     xd = Q.fp8_dequant_1x128(xc, xsc)[:, :D]                  # [T, D] fp32
     order, tok, counts = sort_tokens(indices, E)
     ws = weights.reshape(-1).index_select(0, order)
@@ -109,7 +110,7 @@ def moe_fp8(x, w1, w3, w2, weights, indices, limit, shared=None, return_parts=Fa
             gu = (xe @ w13d[e].t()).to(torch.bfloat16)
             gate, up = gu[:, :I], gu[:, I:]
             h = swiglu(gate.float(), up.float(), limit, ws[pos:pos + c, None]).to(torch.bfloat16)
-            hc, hs = Q.fp8_quant_1x128(h)
+            hc, hs = Q.fp8_quant_1x128(h, ue8m0)
             hd = Q.fp8_dequant_1x128(hc, hs)[:, :I]
             outs[pos:pos + c] = (hd @ w2d[e].t()).to(torch.bfloat16)
             if return_parts:

@@ -15,7 +15,17 @@ def _pad_k(x: torch.Tensor, mult: int) -> torch.Tensor:
     return x
 
 
-def fp8_quant_1x128(x: torch.Tensor):
+def round_scale_ue8m0(s: torch.Tensor) -> torch.Tensor:
+    """ref/kernel.py:22-37 (fast_log2_ceil, fast_pow2, fast_round_scale): 2^ceil(log2(s)) for
+    positive fp32 s, by the same exponent-field arithmetic (exponent + 1 when the mantissa is
+    non-zero)."""
+    bits = s.contiguous().view(torch.int32)
+    e = (bits >> 23) & 0xFF
+    e = e + ((bits & 0x7FFFFF) != 0).to(torch.int32)
+    return (e << 23).view(torch.float32)
+
+
+def fp8_quant_1x128(x: torch.Tensor, ue8m0: bool = False):
     """ref/kernel.py:40-95,98-124 (act_quant, block_size=128, scale_fmt=None, fp32 scale).
 
     amax over each 1x128 block of float(x); amax = max(amax, 1e-4) (:76);
@@ -31,6 +41,8 @@ def fp8_quant_1x128(x: torch.Tensor):
     blocks = xf.view(rows, kpad // 128, 128)
     amax = blocks.abs().amax(-1).clamp_min(1e-4)
     s = amax * torch.tensor(1.0 / FP8_MAX, dtype=torch.float32)
+    if ue8m0:                      # scale_fmt = "ue8m0": ref/kernel.py:77-78 (round_scale=True)
+        s = round_scale_ue8m0(s)
     q = (blocks / s[..., None]).clamp(-FP8_MAX, FP8_MAX).to(torch.float8_e4m3fn)
     return q.view(torch.uint8).reshape(rows, kpad).contiguous(), s.contiguous()
 
@@ -42,7 +54,7 @@ def fp8_dequant_1x128(codes: torch.Tensor, scales: torch.Tensor) -> torch.Tensor
     return (v * scales[..., None]).reshape(rows, kpad)
 
 
-def fp8_quant_128x128(w: torch.Tensor):
+def fp8_quant_128x128(w: torch.Tensor, ue8m0: bool = False):
     """128x128 block quantizer for expert weights [E, N, K].
 
     The reference has none (weights arrive pre-quantised; the consumer is
@@ -60,6 +72,8 @@ def fp8_quant_128x128(w: torch.Tensor):
     blocks = wf.view(E, npad // 128, 128, kpad // 128, 128)
     amax = blocks.abs().amax(dim=(2, 4)).clamp_min(1e-4)
     s = amax * torch.tensor(1.0 / FP8_MAX, dtype=torch.float32)
+    if ue8m0:
+        s = round_scale_ue8m0(s)
     q = (blocks / s[:, :, None, :, None]).clamp(-FP8_MAX, FP8_MAX).to(torch.float8_e4m3fn)
     codes = q.view(torch.uint8).reshape(E, npad, kpad)[:, :N].contiguous()
     return codes, s.contiguous()

@@ -35,7 +35,7 @@ def test_argument_validation_needs_no_gpu():
     lib = _lib.load()
     assert lib.nv41_moe_layout_workspace_bytes(1000, 64) == 4 * 64 * 4
     assert lib.nv41_moe_layout_workspace_bytes(-1, 64) == _lib.ERR_INVALID
-    assert lib.nv41_quant_fp8_1x128(None, 0, None, 5, 128, None, None, 1, 1, None) == _lib.ERR_INVALID
+    assert lib.nv41_quant_fp8_1x128(None, 0, None, 5, 128, None, None, 1, 1, 0, None) == _lib.ERR_INVALID
     assert lib.nv41_quant_nvfp4_1x16(None, 0, 4, 20, 1.0, None, None, None) == _lib.ERR_INVALID
     assert lib.nv41_moe_combine(None, None, None, None, 0, 4, 2, 64, None) == _lib.ERR_INVALID
 

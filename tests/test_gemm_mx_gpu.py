@@ -1,0 +1,79 @@
+"""GPU: the FP8 path with power-of-two (ue8m0) block scales applied by the tensor core
+(tcgen05 kind::mxf8f6f4.block_scale) vs the oracle in the same scale mode.  Codes and scales
+bit-exact; bf16 outputs max rel <= 2e-2, mean rel <= 2e-3."""
+import pytest
+import torch
+
+from nanov41_b200.workloads import make_case
+from oracle import moe as OM
+from oracle import quant as OQ
+
+pytestmark = pytest.mark.gpu
+LIMIT = 10.0
+CASES = {
+    "d8": dict(T=512, E=8, k=2, D=256, I=256),
+    "d12": dict(T=700, E=16, k=2, D=384, I=384),
+    "c2_small": dict(T=1024, E=8, k=6, D=1024, I=1024),
+    "empty_expert": dict(T=300, E=8, k=2, D=256, I=128, empty_expert=3),
+    "wide": dict(T=256, E=4, k=2, D=2048, I=1024),
+}
+
+
+def test_ue8m0_quantizers_bit_exact():
+    from nanov41_b200 import ops
+    gen = torch.Generator().manual_seed(0)
+    x = (torch.randn(257, 384, generator=gen) * torch.logspace(-3, 3, 257)[:, None]).bfloat16()
+    x[0] = 0
+    c, s = ops.quant_fp8_1x128(x.cuda(), ue8m0=True)
+    oc, osc = OQ.fp8_quant_1x128(x, ue8m0=True)
+    assert torch.equal(s.cpu(), osc) and torch.equal(c.cpu(), oc)
+    assert torch.all(torch.frexp(s.cpu())[0] == 0.5)            # exact powers of two
+    w = (torch.randn(3, 256, 384, generator=gen) * 0.05).bfloat16()
+    wc, ws = ops.quant_fp8_128x128(w.cuda(), ue8m0=True)
+    owc, ows = OQ.fp8_quant_128x128(w, ue8m0=True)
+    assert torch.equal(ws.cpu(), ows) and torch.equal(wc.cpu(), owc)
+
+
+@pytest.mark.parametrize("name", list(CASES))
+def test_forward_ue8m0_vs_oracle(name):
+    from nanov41_b200 import ops
+    c = make_case(seed=11, **CASES[name])
+    g = {n: t.cuda() for n, t in c.items()}
+    wq = ops.quantize_expert_weights(g["w1"], g["w3"], g["w2"], ue8m0=True)
+    out, parts = ops.moe_forward_fp8(g["x"], wq, g["weights"], g["indices"], LIMIT,
+                                     return_parts=True)
+    ops.check_status()
+    ref, rp = OM.moe_fp8(c["x"], c["w1"], c["w3"], c["w2"], c["weights"], c["indices"], LIMIT,
+                         return_parts=True, ue8m0=True)
+    lay = parts["layout"]
+    pad_pos = lay.pad_pos.cpu().long()
+    for nm in ("gate", "up", "h"):
+        mx, mean = OM.rel_errors(parts[nm].cpu()[pad_pos], rp[nm])
+        assert mx <= 8e-3 and mean <= 5e-4, (nm, mx, mean)
+    used = int(lay.meta[1].item())
+    hc, hs = OQ.fp8_quant_1x128(parts["h"].cpu()[:used], ue8m0=True)
+    assert torch.equal(parts["h_codes"].cpu()[:used], hc)
+    assert torch.equal(parts["h_scale"].cpu()[:, :used], hs.t().contiguous())
+    mx, mean = OM.rel_errors(parts["y_rows"].cpu()[pad_pos], rp["outs"])
+    assert mx <= 2e-2 and mean <= 2e-3, ("y_rows", mx, mean)
+    mx, mean = OM.rel_errors(out.cpu(), ref)
+    assert mx <= 2e-2 and mean <= 2e-3, ("out", mx, mean)
+
+
+def test_ue8m0_contiguous_and_gathered_activations_agree():
+    from nanov41_b200 import ops
+    c = make_case(seed=5, **CASES["d12"])
+    g = {n: t.cuda() for n, t in c.items()}
+    wq = ops.quantize_expert_weights(g["w1"], g["w3"], g["w2"], ue8m0=True)
+    lay = ops.build_layout(g["indices"].reshape(-1), wq.E, 2, g["weights"].reshape(-1))
+    xc, xs = ops.quant_fp8_1x128(g["x"], scale_kmajor=True, ue8m0=True)
+    a = ops.gemm1_mx(ops.A_GATHER_FP8, xc, xs, None, wq.w13_codes, wq.w13_sf, lay, LIMIT, True, True)
+    xpc, xps = ops.quant_fp8_1x128(g["x"], gather=lay.row_token, scale_kmajor=True, ue8m0=True)
+    b = ops.gemm1_mx(ops.A_CONTIGUOUS, xpc, None, ops.pack_sf_rows(xps), wq.w13_codes, wq.w13_sf,
+                     lay, LIMIT, True, True)
+    ops.check_status()
+    used = int(lay.meta[1].item())
+    assert torch.equal(a[0][:used], b[0][:used]) and torch.equal(a[1][:, :used], b[1][:, :used])
+    assert torch.equal(a[2], b[2])
+    for i in (3, 4, 5):
+        assert torch.equal(a[i][:used], b[i][:used])
