@@ -224,11 +224,11 @@ int nv41_gather_rows_bf16(const void* src, long long src_ld, const int* rows, lo
  * nanov41/triton_grouped_moe.py:759-792 (_swiglu_bwd_kernel, strict clamp masks) and :1243-1262
  * (_moe_dws_kernel).  dact, gate, up: bf16 [P_max, I]; meta from nv41_moe_layout_build.
  * Outputs: dgate, dup bf16 [P_max, I]; dgu_codes e4m3 [P_max, 2I]; dgu_scales fp32
- * [2I/128][P_max]; dws fp32 [P_max].  I % 128 == 0. */
+ * [2I/128][P_max]; dws fp32 [P_max].  I % 128 == 0.  ue8m0 as in nv41_quant_fp8_1x128. */
 int nv41_swiglu_bwd_quant(const void* dact, const void* gate, const void* up,
                           const float* row_weight, const int* meta, int I, long long P_max,
                           float swiglu_limit, void* dgate, void* dup, void* dgu_codes,
-                          float* dgu_scales, float* dws, void* stream);
+                          float* dgu_scales, float* dws, int ue8m0, void* stream);
 
 /* Grouped weight gradient out[e] = A[rows_e]^T @ B[rows_e] (bf16 in, fp32 accumulate in TMEM,
  * bf16 out); nanov41/triton_grouped_moe.py:277-296 (_dw_kernel), :795-862 (_dw13_kernel).

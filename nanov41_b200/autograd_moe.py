@@ -16,19 +16,22 @@ from . import ops
 
 class _RoutedExperts(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, ws, shared, w1, w3, w2, indices, limit, wq):
+    def forward(ctx, x, ws, shared, w1, w3, w2, indices, limit, wq, ue8m0=False):
         T, D = x.shape
         k = indices.shape[1]
         need_grad = any(ctx.needs_input_grad)
         if wq is None:
-            wq = ops.quantize_expert_weights(w1, w3, w2, transposed=need_grad)
+            wq = ops.quantize_expert_weights(w1, w3, w2, transposed=need_grad, ue8m0=ue8m0)
         layout = ops.build_layout(indices.reshape(-1), wq.E, k, ws.reshape(-1))
         x = x.contiguous()
-        x_codes, x_scale = ops.quant_fp8_1x128(x, scale_kmajor=True)
-        h_codes, h_scale, gate, up, h = ops.gemm1_fp8(
-            ops.A_GATHER_FP8, x_codes, x_scale, wq.w13_codes, wq.w13_scale, layout, limit,
-            save_gate_up=need_grad, save_h=need_grad)
-        y_rows = ops.gemm_fp8(ops.A_CONTIGUOUS, h_codes, h_scale, wq.w2_codes, wq.w2_scale, layout)
+        h_codes, h_scale, h_sf, gate, up, h, _, _ = ops.fp8_gate_up(x, wq, layout, limit,
+                                                                    save=need_grad)
+        if wq.ue8m0:
+            y_rows = ops.gemm_mx(ops.A_CONTIGUOUS, h_codes, None, h_sf, wq.w2_codes, wq.w2_sf,
+                                 layout)
+        else:
+            y_rows = ops.gemm_fp8(ops.A_CONTIGUOUS, h_codes, h_scale, wq.w2_codes, wq.w2_scale,
+                                  layout)
         out = ops.combine(y_rows, layout.row_of_flat, T, k, shared)
         if need_grad:
             ctx.save_for_backward(x, gate, up, h)
@@ -45,14 +48,24 @@ class _RoutedExperts(torch.autograd.Function):
                                 "(quantize_expert_weights(..., transposed=True))")
         T, D = x.shape
         dout = dout.to(torch.bfloat16).contiguous()
-        dq_codes, dq_scale = ops.quant_fp8_1x128(dout, scale_kmajor=True)
-        dact = ops.gemm_fp8(ops.A_GATHER_FP8, dq_codes, dq_scale, wq.w2_codes_t, wq.w2_scale, lay,
-                            b_scale_transposed=True)[:, :wq.I]
+        dq_codes, dq_scale = ops.quant_fp8_1x128(dout, gather=lay.row_token, scale_kmajor=True,
+                                                 ue8m0=wq.ue8m0)
+        if wq.ue8m0:
+            dact = ops.gemm_mx(ops.A_CONTIGUOUS, dq_codes, None, ops.pack_sf_rows(dq_scale),
+                               wq.w2_codes_t, wq.w2_sf_t, lay)[:, :wq.I]
+        else:
+            dact = ops.gemm_fp8(ops.A_CONTIGUOUS, dq_codes, dq_scale, wq.w2_codes_t, wq.w2_scale,
+                                lay, b_scale_transposed=True)[:, :wq.I]
         if not dact.is_contiguous():
             dact = dact.contiguous()
-        dgate, dup, dgu_codes, dgu_scale, dws_rows = ops.swiglu_bwd_quant(dact, gate, up, lay, limit)
-        dx_rows = ops.gemm_fp8(ops.A_CONTIGUOUS, dgu_codes, dgu_scale, wq.w13_codes_t,
-                               wq.w13_scale, lay, b_scale_transposed=True)
+        dgate, dup, dgu_codes, dgu_scale, dws_rows = ops.swiglu_bwd_quant(dact, gate, up, lay, limit,
+                                                                          wq.ue8m0)
+        if wq.ue8m0:
+            dx_rows = ops.gemm_mx(ops.A_CONTIGUOUS, dgu_codes, None, ops.pack_sf_rows(dgu_scale),
+                                  wq.w13_codes_t, wq.w13_sf_t, lay)
+        else:
+            dx_rows = ops.gemm_fp8(ops.A_CONTIGUOUS, dgu_codes, dgu_scale, wq.w13_codes_t,
+                                   wq.w13_scale, lay, b_scale_transposed=True)
         if dx_rows.shape[1] != D:
             dx_rows = dx_rows[:, :D].contiguous()
         dx = ops.combine(dx_rows, lay.row_of_flat, T, lay.k)
@@ -65,14 +78,28 @@ class _RoutedExperts(torch.autograd.Function):
             dw1 = ops.wgrad_bf16(dgate, x_rows, lay)       # [E, I, D]
             dw3 = ops.wgrad_bf16(dup, x_rows, lay)
         dshared = dout if ctx.has_shared else None
-        return dx, dws, dshared, dw1, dw3, dw2, None, None, None
+        return dx, dws, dshared, dw1, dw3, dw2, None, None, None, None
 
 
-def experts_forward(x, ws, indices, w1, w3, w2, limit, shared=None, wq=None):
+SCALE_FMT = None      # module default: None = fp32 block scales, "ue8m0" = power-of-two scales
+
+
+def set_scale_fmt(fmt) -> None:
+    """Block-scale format of the drop-in forwards: None (fp32 scales, ref/kernel.py:80) or
+    "ue8m0" (power-of-two scales, ref/kernel.py:77-78; the reference model's own default)."""
+    global SCALE_FMT
+    if fmt not in (None, "ue8m0"):
+        raise ValueError(f"scale_fmt must be None or 'ue8m0', got {fmt!r}")
+    SCALE_FMT = fmt
+
+
+def experts_forward(x, ws, indices, w1, w3, w2, limit, shared=None, wq=None, scale_fmt="default"):
     """x [T, D] bf16; ws [T, k] fp32; indices [T, k]; w1, w3 [E, I, D], w2 [E, D, I] bf16
     (``[out, in]``); shared: optional bf16 [T, D] added in fp32 before the single rounding.
     Differentiable w.r.t. x, ws, shared, w1, w3, w2."""
-    return _RoutedExperts.apply(x, ws, shared, w1, w3, w2, indices, float(limit or 0.0), wq)
+    fmt = SCALE_FMT if scale_fmt == "default" else scale_fmt
+    return _RoutedExperts.apply(x, ws, shared, w1, w3, w2, indices, float(limit or 0.0), wq,
+                                fmt == "ue8m0")
 
 
 # ------------------------------------------------------------------------------ module glue
@@ -110,10 +137,12 @@ def routed_experts(moe, xf, weights, indices, shared):
     key = _weights_key(experts)
     cached = getattr(moe, _WQ_ATTR, None)
     need_t = torch.is_grad_enabled() and (xf.requires_grad or weights.requires_grad)
-    if cached is None or cached[0] != key or (need_t and cached[1].w2_codes_t is None):
+    ue8m0 = SCALE_FMT == "ue8m0"
+    if (cached is None or cached[0] != key or cached[1].ue8m0 != ue8m0
+            or (need_t and cached[1].w2_codes_t is None)):
         with torch.no_grad():
             w1, w3, w2 = stacked_weights(experts)
-            cached = (key, ops.quantize_expert_weights(w1, w3, w2, transposed=need_t))
+            cached = (key, ops.quantize_expert_weights(w1, w3, w2, transposed=need_t, ue8m0=ue8m0))
         setattr(moe, _WQ_ATTR, cached)
     wq = cached[1]
     dummy = xf.new_empty(0)

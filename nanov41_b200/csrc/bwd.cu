@@ -67,6 +67,18 @@ __device__ __forceinline__ uint2 quant8(const float (&f)[8], float s) {
   return make_uint2(w[0], w[1]);
 }
 
+// fp32 block scale, or (ue8m0) rounded up to a power of two: ref/kernel.py:22-37,76-80
+__device__ __forceinline__ float block_scale(float amax, int ue8m0) {
+  float s = fmaxf(amax, 1e-4f) * (1.0f / 448.0f);
+  if (ue8m0) {
+    const uint32_t b = __float_as_uint(s);
+    uint32_t e = (b >> 23) & 0xFFu;
+    if (b & 0x7FFFFFu) ++e;
+    s = __uint_as_float(e << 23);
+  }
+  return s;
+}
+
 // One warp per padded row; a half-warp (16 lanes x 8 columns) covers one 1x128 block.
 __global__ void __launch_bounds__(256)
 swiglu_bwd_quant_kernel(const __nv_bfloat16* __restrict__ dact, const __nv_bfloat16* __restrict__ gate,
@@ -74,7 +86,7 @@ swiglu_bwd_quant_kernel(const __nv_bfloat16* __restrict__ dact, const __nv_bfloa
                         const int* __restrict__ meta, int I, long long P_max, float L,
                         __nv_bfloat16* __restrict__ dgate, __nv_bfloat16* __restrict__ dup,
                         uint8_t* __restrict__ codes, float* __restrict__ scales,
-                        float* __restrict__ dws) {
+                        float* __restrict__ dws, int ue8m0) {
   const int lane = threadIdx.x & 31;
   const long long warp0 = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
   const long long nwarps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
@@ -123,8 +135,8 @@ swiglu_bwd_quant_kernel(const __nv_bfloat16* __restrict__ dact, const __nv_bfloa
         am_u = fmaxf(am_u, __shfl_xor_sync(hmask, am_u, o));
       }
       if (in) {
-        const float sg = fmaxf(am_g, 1e-4f) * (1.0f / 448.0f);
-        const float su = fmaxf(am_u, 1e-4f) * (1.0f / 448.0f);
+        const float sg = block_scale(am_g, ue8m0);
+        const float su = block_scale(am_u, ue8m0);
         *reinterpret_cast<uint4*>(dgate + p * I + col) = pack8(dg);
         *reinterpret_cast<uint4*>(dup + p * I + col) = pack8(du);
         *reinterpret_cast<uint2*>(codes + p * 2 * I + col) = quant8(dg, sg);
@@ -162,7 +174,7 @@ extern "C" int nv41_gather_rows_bf16(const void* src, long long src_ld, const in
 extern "C" int nv41_swiglu_bwd_quant(const void* dact, const void* gate, const void* up,
                                      const float* row_weight, const int* meta, int I,
                                      long long P_max, float swiglu_limit, void* dgate, void* dup,
-                                     void* dgu_codes, float* dgu_scales, float* dws,
+                                     void* dgu_codes, float* dgu_scales, float* dws, int ue8m0,
                                      void* stream) {
   if (!dact || !gate || !up || !row_weight || !meta || !dgate || !dup || !dgu_codes ||
       !dgu_scales || !dws || I <= 0 || P_max <= 0)
@@ -175,6 +187,6 @@ extern "C" int nv41_swiglu_bwd_quant(const void* dact, const void* gate, const v
       static_cast<const __nv_bfloat16*>(dact), static_cast<const __nv_bfloat16*>(gate),
       static_cast<const __nv_bfloat16*>(up), row_weight, meta, I, P_max, swiglu_limit,
       static_cast<__nv_bfloat16*>(dgate), static_cast<__nv_bfloat16*>(dup),
-      static_cast<uint8_t*>(dgu_codes), dgu_scales, dws);
+      static_cast<uint8_t*>(dgu_codes), dgu_scales, dws, ue8m0);
   return launch_status();
 }

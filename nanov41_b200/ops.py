@@ -383,7 +383,7 @@ def gather_rows_bytes(src: torch.Tensor, rows: torch.Tensor) -> torch.Tensor:
 
 
 def swiglu_bwd_quant(dact: torch.Tensor, gate: torch.Tensor, up: torch.Tensor,
-                     layout: DeviceLayout, limit: float):
+                     layout: DeviceLayout, limit: float, ue8m0: bool = False):
     """SwiGLU backward on [P_max, I] bf16 rows -> (dgate, dup bf16, [dgate|dup] e4m3 codes
     [P_max, 2I], scales fp32 [2I/128, P_max], dws fp32 [P_max])."""
     _need_cuda(dact, gate, up)
@@ -397,7 +397,7 @@ def swiglu_bwd_quant(dact: torch.Tensor, gate: torch.Tensor, up: torch.Tensor,
     check(_lib.load().nv41_swiglu_bwd_quant(_ptr(dact), _ptr(gate), _ptr(up),
                                             _ptr(layout.row_weight), _ptr(layout.meta), I, P,
                                             float(limit), _ptr(dgate), _ptr(dup), _ptr(codes),
-                                            _ptr(scales), _ptr(dws), _stream()),
+                                            _ptr(scales), _ptr(dws), int(ue8m0), _stream()),
           "nv41_swiglu_bwd_quant")
     return dgate, dup, codes, scales, dws
 
@@ -417,26 +417,51 @@ def wgrad_bf16(a_rows: torch.Tensor, b_rows: torch.Tensor, layout: DeviceLayout)
     return out
 
 
+def fp8_gate_up(x, wq: Fp8ExpertWeights, layout: DeviceLayout, limit: float, save: bool = False,
+                gather_in_gemm: bool = False):
+    """Activation quantisation + gate/up GEMM + SwiGLU + re-quantised h, in either scale mode.
+
+    Default: the rows are quantised straight into the padded expert-major order (the quantizer
+    gathers by ``row_token``) and the GEMM reads them with TMA.  ``gather_in_gemm`` quantises once
+    per token instead and lets the GEMM's producer warps fetch rows by token.
+    Returns (h_codes, h_scale, h_sf | None, gate, up, h, x_codes, x_scale)."""
+    if gather_in_gemm:
+        x_codes, x_scale = quant_fp8_1x128(x, scale_kmajor=True, ue8m0=wq.ue8m0)
+        mode = A_GATHER_FP8
+    else:
+        x_codes, x_scale = quant_fp8_1x128(x, gather=layout.row_token, scale_kmajor=True,
+                                           ue8m0=wq.ue8m0)
+        mode = A_CONTIGUOUS
+    if wq.ue8m0:
+        a_sf = None if gather_in_gemm else pack_sf_rows(x_scale)
+        h_codes, h_scale, h_sf, gate, up, h = gemm1_mx(
+            mode, x_codes, x_scale if gather_in_gemm else None, a_sf, wq.w13_codes, wq.w13_sf,
+            layout, limit, save_gate_up=save, save_h=save)
+    else:
+        h_sf = None
+        h_codes, h_scale, gate, up, h = gemm1_fp8(mode, x_codes, x_scale, wq.w13_codes,
+                                                  wq.w13_scale, layout, limit,
+                                                  save_gate_up=save, save_h=save)
+    return h_codes, h_scale, h_sf, gate, up, h, x_codes, x_scale
+
+
 def moe_forward_fp8(x: torch.Tensor, wq: Fp8ExpertWeights, weights: torch.Tensor,
                     indices: torch.Tensor, limit: float, shared: torch.Tensor | None = None,
-                    layout: DeviceLayout | None = None, return_parts: bool = False):
-    """Routed-experts forward in FP8: quantise x once per token, gate/up GEMM with the rows
-    fetched by token + SwiGLU + re-quantised h, down GEMM, fp32 top-k combine (+ shared)."""
+                    layout: DeviceLayout | None = None, return_parts: bool = False,
+                    gather_in_gemm: bool = False):
+    """Routed-experts forward in FP8 (fp32 or ue8m0 block scales, per ``wq.ue8m0``): activation
+    quantisation, gate/up GEMM + SwiGLU + re-quantised h, down GEMM, fp32 top-k combine
+    (+ shared)."""
     _need_cuda(x, weights, indices)
     T, D = x.shape
     k = indices.shape[1]
     if layout is None:
         layout = build_layout(indices.reshape(-1), wq.E, k, weights.reshape(-1))
-    x_codes, x_scale = quant_fp8_1x128(x.contiguous(), scale_kmajor=True, ue8m0=wq.ue8m0)
+    h_codes, h_scale, h_sf, gate, up, h, x_codes, x_scale = fp8_gate_up(
+        x.contiguous(), wq, layout, limit, save=return_parts, gather_in_gemm=gather_in_gemm)
     if wq.ue8m0:
-        h_codes, h_scale, h_sf, gate, up, h = gemm1_mx(
-            A_GATHER_FP8, x_codes, x_scale, None, wq.w13_codes, wq.w13_sf, layout, limit,
-            save_gate_up=return_parts, save_h=return_parts)
         y_rows = gemm_mx(A_CONTIGUOUS, h_codes, None, h_sf, wq.w2_codes, wq.w2_sf, layout)
     else:
-        h_codes, h_scale, gate, up, h = gemm1_fp8(A_GATHER_FP8, x_codes, x_scale, wq.w13_codes,
-                                                  wq.w13_scale, layout, limit,
-                                                  save_gate_up=return_parts, save_h=return_parts)
         y_rows = gemm_fp8(A_CONTIGUOUS, h_codes, h_scale, wq.w2_codes, wq.w2_scale, layout)
     out = combine(y_rows, layout.row_of_flat, T, k, shared)
     if return_parts:

@@ -172,7 +172,8 @@ def moe_fp8_backward(x, dout, weights, indices, limit, prepared, parts):
     order, tok, counts = parts["order"], parts["tok"], parts["counts"]
     ws = weights.reshape(-1).index_select(0, order)
     dout = dout.to(torch.bfloat16)
-    dq = Q.fp8_dequant_1x128(*Q.fp8_quant_1x128(dout))[:, :D]
+    ue8m0 = prepared.get("ue8m0", False)
+    dq = Q.fp8_dequant_1x128(*Q.fp8_quant_1x128(dout, ue8m0))[:, :D]
     R = T * k
     dx_rows = torch.zeros(R, D, dtype=torch.bfloat16)
     dws_rows = torch.zeros(R)
@@ -191,7 +192,7 @@ def moe_fp8_backward(x, dout, weights, indices, limit, prepared, parts):
             dg, du = dg.to(torch.bfloat16), du.to(torch.bfloat16)
             dws_rows[sl] = dws
             dgu = torch.cat((dg, du), dim=1)
-            dgu_d = Q.fp8_dequant_1x128(*Q.fp8_quant_1x128(dgu))[:, :2 * I]
+            dgu_d = Q.fp8_dequant_1x128(*Q.fp8_quant_1x128(dgu, ue8m0))[:, :2 * I]
             dx_rows[sl] = (dgu_d @ w13d[e]).to(torch.bfloat16)
             dw2[e] = (dout[t].float().t() @ parts["h"][sl].float()).to(torch.bfloat16)
             dw1[e] = (dg.float().t() @ x[t].float()).to(torch.bfloat16)

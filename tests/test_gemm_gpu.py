@@ -46,8 +46,9 @@ def test_forward_fp8_vs_oracle(name):
     lay = parts["layout"]
     D, I = c["x"].shape[1], c["w1"].shape[1]
     # quantised inputs: bit exact
-    assert torch.equal(parts["x_codes"].cpu(), rp["x_codes"])
-    assert torch.equal(parts["x_scale"].cpu(), rp["x_scales"].t().contiguous())
+    pp, tk_ = lay.pad_pos.cpu().long(), rp["tok"]
+    assert torch.equal(parts["x_codes"].cpu()[pp], rp["x_codes"][tk_])
+    assert torch.equal(parts["x_scale"].cpu()[:, pp], rp["x_scales"][tk_].t().contiguous())
     assert torch.equal(wq.w13_codes.cpu(), rp["w13"][0]) and torch.equal(wq.w13_scale.cpu(), rp["w13"][1])
     assert torch.equal(wq.w2_codes.cpu(), rp["w2"][0]) and torch.equal(wq.w2_scale.cpu(), rp["w2"][1])
     pad_pos = lay.pad_pos.cpu().long()           # sorted position -> padded row
@@ -87,6 +88,18 @@ def test_contiguous_and_gathered_activations_agree():
             assert torch.equal(ta[:used], tb[:used])
         else:
             assert torch.equal(ta[:, :used], tb[:, :used])
+
+
+def test_gather_in_gemm_gives_identical_output():
+    from nanov41_b200 import ops
+    c = make_case(seed=8, **CASES["c2_small"])
+    g = {n: t.cuda() for n, t in c.items()}
+    for ue8m0 in (False, True):
+        wq = ops.quantize_expert_weights(g["w1"], g["w3"], g["w2"], ue8m0=ue8m0)
+        a = ops.moe_forward_fp8(g["x"], wq, g["weights"], g["indices"], LIMIT)
+        b = ops.moe_forward_fp8(g["x"], wq, g["weights"], g["indices"], LIMIT, gather_in_gemm=True)
+        ops.check_status()
+        assert torch.equal(a, b)
 
 
 def test_forward_is_deterministic():
