@@ -129,7 +129,9 @@ def workload_config():
                         "top-6 Zipf(1.0) seed 1, D=1024 I=1024, 0.1% x100 outliers",
             "E": 64, "T": 16384, "k": 6, "D": 1024, "I": 1024,
             "l2": "inputs_exceed_l2 (fp8 weights 201 MB + activations > 126 MB L2)",
-            "weights": "block-quantised once outside the timed region"}
+            "weights": "block-quantised once outside the timed region",
+            "scales": "fp32 1x128 / 128x128 block scales (headline); other_modes holds the "
+                      "ue8m0-scale and NVFP4 variants measured in the same run"}
 
 
 # ------------------------------------------------------------------------------ ours
@@ -252,13 +254,14 @@ def run_ours(args):
     T, k, D, I, E = cfg["T"], cfg["k"], cfg["D"], cfg["I"], cfg["E"]
     flops = fwd_flops(T, k, D, I)
     g = {n: t.to(dev) for n, t in c.items()}
-    wq = ops.quantize_expert_weights(g["w1"], g["w3"], g["w2"])
-    del g["w1"], g["w3"], g["w2"]
+    ue8m0 = args.scale_fmt == "ue8m0"
+    wq = ops.quantize_expert_weights(g["w1"], g["w3"], g["w2"], ue8m0=ue8m0)
+    w_bf16 = (g.pop("w1"), g.pop("w3"), g.pop("w2"))
     x_host = c["x"].pin_memory()
     idx_host = c["indices"].pin_memory()
     w_host = c["weights"].pin_memory()
     out_host = torch.empty((T, D), dtype=torch.bfloat16).pin_memory()
-    launches_per_step = 7   # layout x3, act quant, gate/up GEMM, down GEMM, combine
+    launches_per_step = 8   # layout x3, act quant, row permute, 2 GEMMs, combine
 
     def step_device():
         return ops.moe_forward_fp8(g["x"], wq, g["weights"], g["indices"], LIMIT)
@@ -302,7 +305,6 @@ def run_ours(args):
 
     # per-kernel breakdown with events on the launching stream (dominant kernel -> roofline)
     lay = ops.build_layout(g["indices"].reshape(-1), E, k, g["weights"].reshape(-1))
-    xc, xs = ops.quant_fp8_1x128(g["x"], scale_kmajor=True)
     reps = max(3, args.steps)
 
     def time_kernel(fn):
@@ -317,17 +319,61 @@ def run_ours(args):
         torch.cuda.synchronize()
         return sum(ev[i].elapsed_time(ev[i + 1]) for i in range(reps)) / reps
 
-    ms_quant = time_kernel(lambda: ops.quant_fp8_1x128(g["x"], scale_kmajor=True))
+    def fp8_breakdown(w):
+        """CUDA-event time of every kernel of the FP8 forward for expert weights `w`."""
+        u = w.ue8m0
+        xc0, xs0 = ops.quant_fp8_1x128(g["x"], scale_kmajor=True, ue8m0=u)
+        t_quant = time_kernel(lambda: ops.quant_fp8_1x128(g["x"], scale_kmajor=True, ue8m0=u))
+        xc, xs, xsf = ops.gather_fp8_rows(xc0, xs0, lay, u)
+        t_gather = time_kernel(lambda: ops.gather_fp8_rows(xc0, xs0, lay, u))
+        if u:
+            f1 = lambda: ops.gemm1_mx(ops.A_CONTIGUOUS, xc, None, xsf, w.w13_codes, w.w13_sf, lay, LIMIT)
+            hc, hs, hsf = f1()[:3]
+            f2 = lambda: ops.gemm_mx(ops.A_CONTIGUOUS, hc, None, hsf, w.w2_codes, w.w2_sf, lay)
+        else:
+            f1 = lambda: ops.gemm1_fp8(ops.A_CONTIGUOUS, xc, xs, w.w13_codes, w.w13_scale, lay, LIMIT)
+            hc, hs = f1()[:2]
+            f2 = lambda: ops.gemm_fp8(ops.A_CONTIGUOUS, hc, hs, w.w2_codes, w.w2_scale, lay)
+        t1, t2 = time_kernel(f1), time_kernel(f2)
+        y_rows = f2()
+        t_comb = time_kernel(lambda: ops.combine(y_rows, lay.row_of_flat, T, k))
+        return {"act_quant": t_quant, "permute_rows": t_gather, "gemm_gate_up": t1,
+                "gemm_down": t2, "combine": t_comb}
+
     ms_layout = time_kernel(lambda: ops.build_layout(g["indices"].reshape(-1), E, k,
                                                      g["weights"].reshape(-1)))
-    ms_g1 = time_kernel(lambda: ops.gemm1_fp8(ops.A_GATHER_FP8, xc, xs, wq.w13_codes,
-                                              wq.w13_scale, lay, LIMIT))
-    hc, hs, _, _, _ = ops.gemm1_fp8(ops.A_GATHER_FP8, xc, xs, wq.w13_codes, wq.w13_scale, lay,
-                                    LIMIT)
-    ms_g2 = time_kernel(lambda: ops.gemm_fp8(ops.A_CONTIGUOUS, hc, hs, wq.w2_codes, wq.w2_scale,
-                                             lay))
-    y_rows = ops.gemm_fp8(ops.A_CONTIGUOUS, hc, hs, wq.w2_codes, wq.w2_scale, lay)
-    ms_comb = time_kernel(lambda: ops.combine(y_rows, lay.row_of_flat, T, k))
+    kms = fp8_breakdown(wq)
+    ms_g1, ms_g2 = kms["gemm_gate_up"], kms["gemm_down"]
+    kms = dict(layout_x3=ms_layout, **kms)
+
+    # the other scale formats of the path, measured in the same run (not the headline)
+    def other_fmt():
+        w_other = ops.quantize_expert_weights(*w_bf16, ue8m0=not wq.ue8m0)
+        ms = timed(lambda: ops.moe_forward_fp8(g["x"], w_other, g["weights"], g["indices"], LIMIT),
+                   args.steps, args.warmup)
+        br = fp8_breakdown(w_other)
+        return {"scale_fmt": "ue8m0" if w_other.ue8m0 else "fp32", "ms_per_step": ms,
+                "value": flops / (ms * 1e-3) / 1e12, "kernels_ms": br,
+                "gemm_gate_up_tflops": 4.0 * T * k * D * I / (br["gemm_gate_up"] * 1e-3) / 1e12,
+                "gemm_down_tflops": 2.0 * T * k * D * I / (br["gemm_down"] * 1e-3) / 1e12}
+
+    def nvfp4_mode():
+        w4 = ops.quantize_expert_weights_nvfp4(*w_bf16)
+        ms = timed(lambda: ops.moe_forward_nvfp4(g["x"], w4, g["weights"], g["indices"], LIMIT),
+                   args.steps, args.warmup)
+        xp, xsf = ops.quant_nvfp4_tc(g["x"], 1.0, gather=lay.row_token)
+        f1 = lambda: ops.gemm_nvfp4(xp, xsf, 1.0, w4.w13_packed, w4.w13_sf, w4.w13_global, E, 2 * I, lay)
+        hp, hsf = ops.swiglu_quant_nvfp4(f1(), lay, LIMIT)
+        f2 = lambda: ops.gemm_nvfp4(hp, hsf, 1.0, w4.w2_packed, w4.w2_sf, w4.w2_global, E, D, lay)
+        t1, t2 = time_kernel(f1), time_kernel(f2)
+        return {"ms_per_step": ms, "value": flops / (ms * 1e-3) / 1e12,
+                "gemm_gate_up_tflops": 4.0 * T * k * D * I / (t1 * 1e-3) / 1e12,
+                "gemm_down_tflops": 2.0 * T * k * D * I / (t2 * 1e-3) / 1e12,
+                "frac_of_fp4_spec_9000": 4.0 * T * k * D * I / (t1 * 1e-3) / 1e12 / 9000.0}
+
+    other_modes = {}
+    if world == 1:
+        other_modes = {"fp8_other_scale_fmt": other_fmt(), "nvfp4_w4a4": nvfp4_mode()}
     ops.check_status()
 
     if rank != 0:
@@ -358,14 +404,16 @@ def run_ours(args):
                 "d2h_bytes_per_step": out_host.numel() * 2},
         "gpu_launches": launches_per_step * args.steps,
         "clocks": clocks,
-        "roofline": {"bound": "tensor", "kernel": "grouped_gemm_fp8_kernel<gather,swiglu> (gate/up)",
+        "scale_fmt": args.scale_fmt, "other_modes": other_modes,
+        "roofline": {"bound": "tensor",
+                     "kernel": ("gemm_mx_kernel<tma,swiglu>" if ue8m0 else
+                                "grouped_gemm_fp8_kernel<tma,swiglu>") + " (gate/up)",
                      "achieved": achieved, "peak": fp8_peak, "unit": "TFLOP/s",
                      "frac": achieved / fp8_peak, "traffic": None,
                      "peak_note": f"2 x bf16 burst {bf16_peak} TFLOP/s {peak_src} "
                                   f"(no measured fp8 figure); {achieved / SPEC_FP8_TFLOPS:.3f} of "
                                   f"the 4500 TFLOP/s dense-fp8 spec"},
-        "kernels_ms": {"layout_x3": ms_layout, "act_quant": ms_quant, "gemm_gate_up": ms_g1,
-                       "gemm_down": ms_g2, "combine": ms_comb},
+        "kernels_ms": kms,
         "kernel_tflops": {"gemm_gate_up": achieved,
                           "gemm_down": 2.0 * T * k * D * I / (ms_g2 * 1e-3) / 1e12},
         "moe_layer_tokens_per_s": world * T / (ms_dev * 1e-3),
@@ -383,6 +431,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--cpu-sample-tokens", type=int, default=16384)
+    ap.add_argument("--scale-fmt", default="fp32", choices=["fp32", "ue8m0"],
+                    help="FP8 block-scale format of the headline run (BASELINE config 2: fp32)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -212,6 +212,16 @@ int nv41_moe_gemm_nvfp4(const void* a_packed, const void* a_sf, float a_global,
                         int N, int Kpad, const int* tile_expert, long long P_max, void* c_out,
                         long long c_ld, unsigned* status, void* stream);
 
+/* Expert-major copy of FP8 rows quantised once per token (the permute of
+ * nanov41/fast_moe.py:399 / triton_grouped_moe.py:1507-1509 applied to codes and scales):
+ * codes_rows[p] = codes[row_token[p]], scales_rows[kb][p] = scales[kb][row_token[p]]; padding
+ * rows get zero codes and scale 1.  sf_atoms (optional, ue8m0 scales only): the e8m0 scale atoms
+ * [P_max/128][K/128][512] of those rows.  codes: u8 [T, ld]; K % 128 == 0. */
+int nv41_gather_fp8_rows(const void* codes, long long ld, const float* scales_kmajor,
+                         long long scale_kb_stride, const int* row_token, const int* meta, int K,
+                         long long P_max, void* codes_rows, float* scales_rows_kmajor,
+                         void* sf_atoms, void* stream);
+
 /* ---- backward ------------------------------------------------------------------------------ */
 
 /* dst[p] = src[rows[p]] (a zero row where rows[p] < 0); bf16, cols % 8 == 0.  Materialises the

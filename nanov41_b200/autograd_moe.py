@@ -48,10 +48,10 @@ class _RoutedExperts(torch.autograd.Function):
                                 "(quantize_expert_weights(..., transposed=True))")
         T, D = x.shape
         dout = dout.to(torch.bfloat16).contiguous()
-        dq_codes, dq_scale = ops.quant_fp8_1x128(dout, gather=lay.row_token, scale_kmajor=True,
-                                                 ue8m0=wq.ue8m0)
+        dq_codes, dq_scale = ops.quant_fp8_1x128(dout, scale_kmajor=True, ue8m0=wq.ue8m0)
+        dq_codes, dq_scale, dq_sf = ops.gather_fp8_rows(dq_codes, dq_scale, lay, wq.ue8m0)
         if wq.ue8m0:
-            dact = ops.gemm_mx(ops.A_CONTIGUOUS, dq_codes, None, ops.pack_sf_rows(dq_scale),
+            dact = ops.gemm_mx(ops.A_CONTIGUOUS, dq_codes, None, dq_sf,
                                wq.w2_codes_t, wq.w2_sf_t, lay)[:, :wq.I]
         else:
             dact = ops.gemm_fp8(ops.A_CONTIGUOUS, dq_codes, dq_scale, wq.w2_codes_t, wq.w2_scale,

@@ -36,6 +36,41 @@ gather_rows_kernel(const uint4* __restrict__ src, long long src_ld16, const int*
   }
 }
 
+// Expert-major copy of per-token FP8 rows: codes_rows[p] = codes[row_token[p]] (zeros for padding
+// rows), scales_rows[kb][p] = scales[kb][row_token[p]] (1.0 for padding rows) and, when `atoms`
+// is given, the e8m0 exponent bytes of those (power-of-two) scales in the 512-byte tensor-core
+// atoms atoms[p/128][kb][(r%32)*16 + (r/32)*4 + j].  One warp per padded row.
+// (x_sorted = x[layout.tok], nanov41/triton_grouped_moe.py:1507-1509, on quantised rows.)
+__global__ void __launch_bounds__(256)
+gather_fp8_rows_kernel(const uint8_t* __restrict__ codes, long long ld, const float* __restrict__ scales,
+                       long long s_kb_stride, const int* __restrict__ row_token,
+                       const int* __restrict__ meta, int K, uint8_t* __restrict__ codes_rows,
+                       float* __restrict__ scales_rows, long long P_max, uint8_t* __restrict__ atoms) {
+  const int lane = threadIdx.x & 31;
+  const long long warp0 = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const long long nwarps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
+  const long long used = meta[1];
+  const int nkb = K / 128, chunks = K / 16;
+  for (long long p = warp0; p < used; p += nwarps) {
+    const int tok = row_token[p];
+    for (int c = lane; c < chunks; c += 32) {
+      uint4 v = make_uint4(0u, 0u, 0u, 0u);
+      if (tok >= 0) v = __ldg(reinterpret_cast<const uint4*>(codes + tok * ld) + c);
+      reinterpret_cast<uint4*>(codes_rows + p * K)[c] = v;
+    }
+    for (int kb = lane; kb < nkb; kb += 32) {
+      const float s = tok >= 0 ? __ldg(scales + kb * s_kb_stride + tok) : 1.0f;
+      scales_rows[kb * P_max + p] = s;
+      if (atoms) {
+        const uint32_t byte = (__float_as_uint(s) >> 23) & 0xFFu;
+        const int r = static_cast<int>(p & 127);
+        *reinterpret_cast<uint32_t*>(atoms + ((p >> 7) * nkb + kb) * 512 + (r & 31) * 16 + (r >> 5) * 4) =
+            byte * 0x01010101u;
+      }
+    }
+  }
+}
+
 __device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
   const uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
@@ -168,6 +203,21 @@ extern "C" int nv41_gather_rows_bf16(const void* src, long long src_ld, const in
   gather_rows_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const uint4*>(src), src_ld / 8, rows, static_cast<uint4*>(dst), n_rows,
       cols / 8);
+  return launch_status();
+}
+
+extern "C" int nv41_gather_fp8_rows(const void* codes, long long ld, const float* scales_kmajor,
+                                    long long scale_kb_stride, const int* row_token,
+                                    const int* meta, int K, long long P_max, void* codes_rows,
+                                    float* scales_rows_kmajor, void* sf_atoms, void* stream) {
+  if (!codes || !scales_kmajor || !row_token || !meta || !codes_rows || !scales_rows_kmajor ||
+      K <= 0 || (K % 128) != 0 || P_max <= 0 || (P_max % 128) != 0 || ld < K || (ld % 16) != 0)
+    return NV41_ERR_INVALID;
+  long long blocks = (P_max + 7) / 8;
+  if (blocks > 148LL * 16) blocks = 148LL * 16;
+  gather_fp8_rows_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint8_t*>(codes), ld, scales_kmajor, scale_kb_stride, row_token, meta, K,
+      static_cast<uint8_t*>(codes_rows), scales_rows_kmajor, P_max, static_cast<uint8_t*>(sf_atoms));
   return launch_status();
 }
 

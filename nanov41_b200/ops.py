@@ -375,6 +375,24 @@ def gather_rows(src: torch.Tensor, rows: torch.Tensor) -> torch.Tensor:
     return out
 
 
+def gather_fp8_rows(codes: torch.Tensor, scales_kmajor: torch.Tensor, layout: DeviceLayout,
+                    with_atoms: bool = False):
+    """Per-token FP8 rows -> padded expert-major order: (codes [P_max, K], scales [K/128, P_max],
+    e8m0 scale atoms | None)."""
+    _need_cuda(codes, scales_kmajor)
+    T, K = codes.shape
+    P = layout.P_max
+    dev = codes.device
+    out = torch.empty((P, K), dtype=torch.uint8, device=dev)
+    sc = torch.empty((K // 128, P), dtype=torch.float32, device=dev)
+    atoms = torch.zeros(P // 128 * (K // 128) * 512, dtype=torch.uint8, device=dev) if with_atoms else None
+    check(_lib.load().nv41_gather_fp8_rows(_ptr(codes), codes.stride(0), _ptr(scales_kmajor),
+                                           scales_kmajor.stride(0), _ptr(layout.row_token),
+                                           _ptr(layout.meta), K, P, _ptr(out), _ptr(sc),
+                                           _ptr(atoms), _stream()), "nv41_gather_fp8_rows")
+    return out, sc, atoms
+
+
 def gather_rows_bytes(src: torch.Tensor, rows: torch.Tensor) -> torch.Tensor:
     """Row gather of a uint8 matrix whose row length is a multiple of 16 bytes."""
     if src.dtype != torch.uint8 or src.shape[1] % 16:
@@ -421,19 +439,16 @@ def fp8_gate_up(x, wq: Fp8ExpertWeights, layout: DeviceLayout, limit: float, sav
                 gather_in_gemm: bool = False):
     """Activation quantisation + gate/up GEMM + SwiGLU + re-quantised h, in either scale mode.
 
-    Default: the rows are quantised straight into the padded expert-major order (the quantizer
-    gathers by ``row_token``) and the GEMM reads them with TMA.  ``gather_in_gemm`` quantises once
-    per token instead and lets the GEMM's producer warps fetch rows by token.
+    x is quantised once per token.  Default: the quantised rows are then copied into the padded
+    expert-major order and the GEMM reads them with TMA; ``gather_in_gemm`` skips the copy and
+    lets the GEMM's producer warps fetch rows by token.
     Returns (h_codes, h_scale, h_sf | None, gate, up, h, x_codes, x_scale)."""
-    if gather_in_gemm:
-        x_codes, x_scale = quant_fp8_1x128(x, scale_kmajor=True, ue8m0=wq.ue8m0)
-        mode = A_GATHER_FP8
-    else:
-        x_codes, x_scale = quant_fp8_1x128(x, gather=layout.row_token, scale_kmajor=True,
-                                           ue8m0=wq.ue8m0)
+    x_codes, x_scale = quant_fp8_1x128(x, scale_kmajor=True, ue8m0=wq.ue8m0)   # once per token
+    a_sf, mode = None, A_GATHER_FP8
+    if not gather_in_gemm:
+        x_codes, x_scale, a_sf = gather_fp8_rows(x_codes, x_scale, layout, with_atoms=wq.ue8m0)
         mode = A_CONTIGUOUS
     if wq.ue8m0:
-        a_sf = None if gather_in_gemm else pack_sf_rows(x_scale)
         h_codes, h_scale, h_sf, gate, up, h = gemm1_mx(
             mode, x_codes, x_scale if gather_in_gemm else None, a_sf, wq.w13_codes, wq.w13_sf,
             layout, limit, save_gate_up=save, save_h=save)
