@@ -236,6 +236,67 @@ def run_ep(args, world, rank, local, dev):
     dist.destroy_process_group()
 
 
+STACKS = {
+    # nanov41/configs.py:81-134: MoE layers of the d8 / d12 configs (dim, moe_inter_dim, experts,
+    # top-k, layers) at the batch BASELINE configs 3 / 4 name
+    "d8": dict(L=8, D=256, I=256, E=8, k=2, T=16 * 1024, mode="fp8 forward+backward"),
+    "d12": dict(L=12, D=384, I=384, E=16, k=2, T=32 * 1024, mode="nvfp4 (W4A4) forward"),
+}
+
+
+def run_stack(args, name):
+    """BASELINE configs 3 / 4 restricted to the path that is built here: the routed-expert part
+    of every MoE layer of the d8 / d12 model (the attention / mHC / head around it are not)."""
+    from nanov41_b200 import autograd_moe, ops
+    st = STACKS[name]
+    L, D, I, E, k, T = (st[n] for n in ("L", "D", "I", "E", "k", "T"))
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    layers = []
+    for layer in range(L):
+        c = make_case(T=T, E=E, k=k, D=D, I=I, seed=layer, zipf=False, outliers=False, device=dev)
+        layers.append(c)
+    fwd = fwd_flops(T, k, D, I) * L
+    if name == "d8":
+        for c in layers:
+            for n in ("x", "w1", "w3", "w2", "weights"):
+                c[n].requires_grad_(True)
+
+        def step():
+            for c in layers:
+                y = autograd_moe.experts_forward(c["x"], c["weights"], c["indices"], c["w1"],
+                                                 c["w3"], c["w2"], LIMIT)
+                y.backward(c["x"].detach())
+        flops, launches = 3.0 * fwd, 26 * L
+    else:
+        wqs = [ops.quantize_expert_weights_nvfp4(c["w1"], c["w3"], c["w2"]) for c in layers]
+
+        def step():
+            for c, w in zip(layers, wqs):
+                ops.moe_forward_nvfp4(c["x"], w, c["weights"], c["indices"], LIMIT)
+        flops, launches = fwd, 9 * L
+    for _ in range(args.warmup):
+        step()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    ops.check_status()
+    ms = e0.elapsed_time(e1) / args.steps
+    print(json.dumps({
+        "metric": "expert_gemm_tflops", "value": flops / (ms * 1e-3) / 1e12, "unit": "TFLOP/s",
+        "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": st["mode"], "data": "synthetic",
+        "config": {"workload": f"{name}: routed experts of the {L} MoE layers, {T} tokens, D={D} "
+                               f"I={I} E={E} top-{k}, uniform routing", **st},
+        "moe_layer_tokens_per_s": T / (ms * 1e-3), "gpu_launches": launches * args.steps}),
+        flush=True)
+
+
 def run_ours(args):
     import torch.distributed as dist
     from nanov41_b200 import ops
@@ -431,6 +492,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--cpu-sample-tokens", type=int, default=16384)
+    ap.add_argument("--workload", default="c2", choices=["c2", "d8", "d12"],
+                    help="c2 = BASELINE config 2 (headline); d8 / d12 = expert stacks of configs 3 / 4")
     ap.add_argument("--scale-fmt", default="fp32", choices=["fp32", "ue8m0"],
                     help="FP8 block-scale format of the headline run (BASELINE config 2: fp32)")
     args = ap.parse_args()
@@ -439,7 +502,10 @@ def main():
     else:
         if not torch.cuda.is_available():
             raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback)")
-        run_ours(args)
+        if args.workload != "c2" and int(os.environ.get("WORLD_SIZE", "1")) == 1:
+            run_stack(args, args.workload)
+        else:
+            run_ours(args)
 
 
 if __name__ == "__main__":

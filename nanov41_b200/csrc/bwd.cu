@@ -18,6 +18,7 @@
 #include <cstdint>
 
 #include "../../include/nanov41_b200.h"
+#include "quant_math.cuh"
 #include "util.cuh"
 
 namespace nv41 {
@@ -89,17 +90,9 @@ __device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
   return make_uint4(o[0], o[1], o[2], o[3]);
 }
 __device__ __forceinline__ uint2 quant8(const float (&f)[8], float s) {
-  uint32_t w[2];
-#pragma unroll
-  for (int h = 0; h < 2; ++h) {
-    float q[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) q[i] = fminf(fmaxf(__fdiv_rn(f[4 * h + i], s), -448.f), 448.f);
-    const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(q[0], q[1]), __NV_SATFINITE, __NV_E4M3);
-    const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(q[2], q[3]), __NV_SATFINITE, __NV_E4M3);
-    w[h] = lo | (hi << 16);
-  }
-  return make_uint2(w[0], w[1]);
+  const float r = __frcp_rn(s);
+  return make_uint2(e4m3x4_div(f[0], f[1], f[2], f[3], s, r),
+                    e4m3x4_div(f[4], f[5], f[6], f[7], s, r));
 }
 
 // fp32 block scale, or (ue8m0) rounded up to a power of two: ref/kernel.py:22-37,76-80

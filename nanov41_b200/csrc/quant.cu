@@ -16,6 +16,7 @@
 #include <cstdint>
 
 #include "../../include/nanov41_b200.h"
+#include "quant_math.cuh"
 #include "util.cuh"
 
 namespace nv41 {
@@ -44,15 +45,10 @@ __device__ __forceinline__ float block_scale(float amax, int ue8m0) {
   return s;
 }
 
-// e4m3 code of clamp(x / s, +-448), round-to-nearest-even, saturating.
-__device__ __forceinline__ uint32_t fp8x4_codes(float a, float b, float c, float d, float s) {
-  float q0 = fminf(fmaxf(__fdiv_rn(a, s), -448.f), 448.f);
-  float q1 = fminf(fmaxf(__fdiv_rn(b, s), -448.f), 448.f);
-  float q2 = fminf(fmaxf(__fdiv_rn(c, s), -448.f), 448.f);
-  float q3 = fminf(fmaxf(__fdiv_rn(d, s), -448.f), 448.f);
-  uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(q0, q1), __NV_SATFINITE, __NV_E4M3);
-  uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(q2, q3), __NV_SATFINITE, __NV_E4M3);
-  return lo | (hi << 16);
+// e4m3 code of clamp(x / s, +-448), round-to-nearest-even, saturating (r = RN(1 / s)).
+__device__ __forceinline__ uint32_t fp8x4_codes(float a, float b, float c, float d, float s,
+                                                float r) {
+  return e4m3x4_div(a, b, c, d, s, r);
 }
 
 // ------------------------------------------------------------------------- FP8 1x128 rows
@@ -91,9 +87,10 @@ quant_fp8_1x128_kernel(const __nv_bfloat16* __restrict__ x, long long ld_x,
 #pragma unroll
     for (int o = 8; o >= 1; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(hmask, amax, o));
     const float s = block_scale(amax, ue8m0);
+    const float r = __frcp_rn(s);
     uint2 out;
-    out.x = fp8x4_codes(f[0], f[1], f[2], f[3], s);
-    out.y = fp8x4_codes(f[4], f[5], f[6], f[7], s);
+    out.x = fp8x4_codes(f[0], f[1], f[2], f[3], s, r);
+    out.y = fp8x4_codes(f[4], f[5], f[6], f[7], s, r);
     *reinterpret_cast<uint2*>(codes + row * Kpad + kb * 128 + sub * 8) = out;
     if (sub == 0) scales[row * ss_row + kb * ss_kb] = s;
   }
@@ -146,13 +143,14 @@ quant_fp8_128x128_kernel(const __nv_bfloat16* __restrict__ w, int E, int N, int 
   }
   __syncthreads();
   const float s = s_scale;
+  const float rcp = __frcp_rn(s);
 #pragma unroll
   for (int p = 0; p < 8; ++p) {
     const int rl = p * 16 + r0;
     const int r = nb * 128 + rl;
     uint2 out;
-    out.x = fp8x4_codes(f[p][0], f[p][1], f[p][2], f[p][3], s);
-    out.y = fp8x4_codes(f[p][4], f[p][5], f[p][6], f[p][7], s);
+    out.x = fp8x4_codes(f[p][0], f[p][1], f[p][2], f[p][3], s, rcp);
+    out.y = fp8x4_codes(f[p][4], f[p][5], f[p][6], f[p][7], s, rcp);
     if (r < N) {
       *reinterpret_cast<uint2*>(codes + (static_cast<long long>(e) * N + r) * Kpad + col) = out;
     }
