@@ -312,34 +312,42 @@ __device__ __forceinline__ void role_promote(const GemmArgs& g, const SM& sm, ui
       if (!mbar_wait<40>(sm.tfull(b), tph, sm.abort_flag(), g.status, ST_TIMEOUT_TMEM_FULL)) return;
       tc_fence_after_sync();
       const uint32_t tb = lane_base + b * kBN;
-      // piece c (16 columns): SwiGLU -> gate columns half*64 + 16c (c < 4), up columns
-      // 128 + half*64 + 16(c-4); store -> columns half*128 + 16c
-      auto col = [&](int c) -> uint32_t {
-        return (EPI == EPI_SWIGLU) ? static_cast<uint32_t>((c >> 2) * 128 + half * 64 + (c & 3) * 16)
-                                   : static_cast<uint32_t>(half * 128 + c * 16);
-      };
-      uint32_t va[16], vb[16];
-      tmem_ld_32x32b_x16(tb + col(0), va);
+      if (EPI == EPI_STORE) {
+        // plain tiles have no SwiGLU warps, so these warps own more registers: 64-column pieces,
+        // two TMEM round trips per K block
+        uint32_t wa[64];
 #pragma unroll
-      for (int c = 0; c < 8; c += 2) {
-        const float fa = (EPI == EPI_SWIGLU && c >= 4) ? f1 : f0;
-        tmem_ld_wait_x16(va);
-        tmem_ld_32x32b_x16(tb + col(c + 1), vb);
+        for (int c = 0; c < 2; ++c) {
+          tmem_ld_32x32b_x64(tb + half * 128 + c * 64, wa);
+          tmem_ld_wait_x64(wa);
+          if (c == 1) {
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(sm.tempty(b));
+          }
 #pragma unroll
-        for (int i = 0; i < 16; ++i)
-          acc[c * 16 + i] = fmaf(__uint_as_float(va[i]), fa, acc[c * 16 + i]);
-        tmem_ld_wait_x16(vb);
-        if (c + 2 < 8) {
-          tmem_ld_32x32b_x16(tb + col(c + 2), va);
-        } else {
+          for (int i = 0; i < 64; ++i)
+            acc[c * 64 + i] = fmaf(__uint_as_float(wa[i]), f0, acc[c * 64 + i]);
+        }
+        continue;
+      }
+      // gate|up tiles: 32-column pieces (gate half*64 + {0,32}, then up 128 + half*64 + {0,32});
+      // fewer, larger TMEM reads cost less than many small overlapped ones
+      uint32_t va[32];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const float fa = (c >= 2) ? f1 : f0;
+        tmem_ld_32x32b_x32(tb + (c >> 1) * 128 + half * 64 + (c & 1) * 32, va);
+        tmem_ld_wait_x32(va);
+        if (c == 3) {
           // every piece of this buffer is in registers: hand it back to the UMMA warp
           tc_fence_before_sync();
           __syncwarp();
           if (lane == 0) mbar_arrive(sm.tempty(b));
         }
 #pragma unroll
-        for (int i = 0; i < 16; ++i)
-          acc[(c + 1) * 16 + i] = fmaf(__uint_as_float(vb[i]), fa, acc[(c + 1) * 16 + i]);
+        for (int i = 0; i < 32; ++i)
+          acc[c * 32 + i] = fmaf(__uint_as_float(va[i]), fa, acc[c * 32 + i]);
       }
     }
 
@@ -502,10 +510,14 @@ grouped_gemm_fp8_kernel(const __grid_constant__ GemmArgs g) {
       role_gather<MODE_A>(g, sm, warp - 2, lane, NS);
     }
   } else if (wg == 1) {
-    setmaxnreg_dec<112>();
-    if (EPI == EPI_SWIGLU) role_swiglu(g, sm, warp - 4, lane);
+    if (EPI == EPI_SWIGLU) {
+      setmaxnreg_dec<112>();
+      role_swiglu(g, sm, warp - 4, lane);
+    } else {
+      setmaxnreg_dec<24>();
+    }
   } else {
-    setmaxnreg_inc<168>();
+    if (EPI == EPI_SWIGLU) setmaxnreg_inc<168>(); else setmaxnreg_inc<208>();
     role_promote<MODE_A, EPI>(g, sm, tmem_base, warp - 8, lane);
   }
 
