@@ -163,7 +163,7 @@ def run_ep(args, world, rank, local, dev):
     w1 = torch.stack([expert_weight(e, (I, D), D, 1) for e in ids])
     w3 = torch.stack([expert_weight(e, (I, D), D, 2) for e in ids])
     w2 = torch.stack([expert_weight(e, (D, I), I, 3) for e in ids])
-    wq = ops.quantize_expert_weights(w1, w3, w2)
+    wq = ops.quantize_expert_weights(w1, w3, w2, ue8m0=args.scale_fmt == "ue8m0")
     del w1, w3, w2
     gen.manual_seed(C5["seed"] * 7919 + rank)
     x = torch.randn(T, D, generator=gen, device=dev).bfloat16()
@@ -177,13 +177,14 @@ def run_ep(args, world, rank, local, dev):
     out_host = torch.empty((T, D), dtype=torch.bfloat16).pin_memory()
 
     def step_device():
-        return ep.moe_forward_fp8_ep(x, wq, weights, indices, E, LIMIT)
+        return ep.moe_forward_fp8_ep(x, wq, weights, indices, E, LIMIT, chunks=args.ep_chunks)
 
     def step_e2e():
         xd = x_host.to(dev, non_blocking=True)
         idd = idx_host.to(dev, non_blocking=True)
         wd = w_host.to(dev, non_blocking=True)
-        out_host.copy_(ep.moe_forward_fp8_ep(xd, wq, wd, idd, E, LIMIT), non_blocking=True)
+        out_host.copy_(ep.moe_forward_fp8_ep(xd, wq, wd, idd, E, LIMIT, chunks=args.ep_chunks),
+                       non_blocking=True)
 
     def timed(fn, steps, warmup):
         for _ in range(warmup):
@@ -208,6 +209,48 @@ def run_ep(args, world, rank, local, dev):
     ms_e2e = timed(step_e2e, args.steps, max(1, args.warmup // 2))
     clocks = sampler.stop() if rank == 0 else {}
     ops.check_status()
+    same_1gpu = None
+    if rank == 0:
+        # the same 131,072-token workload on this one GPU (all experts local, no all-to-all), so the
+        # line carries its own single-GPU reference for the expert-parallel number
+        del wq
+        torch.cuda.empty_cache()
+        parts = []
+        for lo in range(0, E, 32):
+            ids_ = range(lo, lo + 32)
+            parts.append(ops.quantize_expert_weights(
+                torch.stack([expert_weight(e, (I, D), D, 1) for e in ids_]),
+                torch.stack([expert_weight(e, (I, D), D, 2) for e in ids_]),
+                torch.stack([expert_weight(e, (D, I), I, 3) for e in ids_]),
+                ue8m0=args.scale_fmt == "ue8m0"))
+        cat = lambda n: None if getattr(parts[0], n) is None else torch.cat([getattr(p, n) for p in parts])
+        wq_all = ops.Fp8ExpertWeights(cat("w13_codes"), cat("w13_scale"), cat("w2_codes"),
+                                      cat("w2_scale"), E, I, D, None, None, parts[0].ue8m0,
+                                      cat("w13_sf"), cat("w2_sf"))
+        del parts
+        xs_, is_, ws_ = [], [], []
+        for r in range(world):
+            gen.manual_seed(C5["seed"] * 7919 + r)
+            xs_.append(torch.randn(T, D, generator=gen, device=dev).bfloat16())
+            is_.append(torch.randn(T, E, generator=gen, device=dev).topk(k, dim=-1)[1])
+            w_ = torch.rand(T, k, generator=gen, device=dev) + 0.05
+            ws_.append((w_ / w_.sum(-1, keepdim=True) * 1.5).float())
+        xa, ia, wa = torch.cat(xs_), torch.cat(is_), torch.cat(ws_)
+        del xs_, is_, ws_
+        for _ in range(2):
+            ops.moe_forward_fp8(xa, wq_all, wa, ia, LIMIT)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(3):
+            ops.moe_forward_fp8(xa, wq_all, wa, ia, LIMIT)
+        e1.record()
+        torch.cuda.synchronize()
+        ms1 = e0.elapsed_time(e1) / 3
+        same_1gpu = {"ms_per_step": ms1, "value": fwd_flops(C5["T"], k, D, I) / (ms1 * 1e-3) / 1e12,
+                     "unit": "TFLOP/s", "note": "config 5 on one GPU, all 256 experts local"}
+        ops.check_status()
+    dist.barrier()
     if rank == 0:
         flops = fwd_flops(C5["T"], k, D, I)
         peaks = json.loads((ROOT / "MEASURED_PEAKS.json").read_text()) \
@@ -219,7 +262,7 @@ def run_ep(args, world, rank, local, dev):
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_dev,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "fp8_e4m3 (fp32 accumulate, bf16 out)", "data": "synthetic",
-            "config": c5_config(world),
+            "config": dict(c5_config(world), ep_chunks=args.ep_chunks), "scale_fmt": args.scale_fmt,
             "e2e": {"value": flops / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s",
                     "ms_per_step": ms_e2e,
                     "h2d_bytes_per_step": x_host.numel() * 2 + idx_host.numel() * 8 + w_host.numel() * 4,
@@ -230,6 +273,7 @@ def run_ep(args, world, rank, local, dev):
                          "frac": tfl / world / (2.0 * bf16_peak), "traffic": None,
                          "peak_note": "per-GPU share of the step vs 2 x measured bf16 burst"},
             "moe_layer_tokens_per_s": C5["T"] / (ms_dev * 1e-3),
+            "same_workload_1gpu": same_1gpu,
             "cpu_baseline": None,
         }
         print(json.dumps(line), flush=True)
@@ -492,6 +536,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--cpu-sample-tokens", type=int, default=16384)
+    ap.add_argument("--ep-chunks", type=int, default=1,
+                    help="N > 1: token slices whose all-to-alls overlap the previous slice's GEMMs")
     ap.add_argument("--workload", default="c2", choices=["c2", "d8", "d12"],
                     help="c2 = BASELINE config 2 (headline); d8 / d12 = expert stacks of configs 3 / 4")
     ap.add_argument("--scale-fmt", default="fp32", choices=["fp32", "ue8m0"],

@@ -77,13 +77,46 @@ def give_back(plan: DispatchPlan, rows: torch.Tensor, group=None) -> torch.Tenso
     return exchange(rows, plan.recv_counts, plan.send_counts, group)
 
 
+def _local_experts(r_codes, r_scale, r_meta, wq_local, e_local, limit, D):
+    """Grouped FP8 expert FFN on received rows (each row is its own token, k = 1); returns the
+    bf16 results in arrival order."""
+    if r_codes.shape[0] == 0:
+        return torch.empty((0, D), dtype=torch.bfloat16, device=r_codes.device)
+    lay = ops.build_layout(r_meta[:, 0].contiguous(), e_local, 1,
+                           r_meta[:, 1].contiguous().view(torch.float32))
+    a_codes, a_scale, a_sf = ops.gather_fp8_rows(r_codes, r_scale.t().contiguous(), lay,
+                                                 with_atoms=wq_local.ue8m0)
+    if wq_local.ue8m0:
+        h_codes, _, h_sf, _, _, _ = ops.gemm1_mx(ops.A_CONTIGUOUS, a_codes, None, a_sf,
+                                                 wq_local.w13_codes, wq_local.w13_sf, lay, limit)
+        y_rows = ops.gemm_mx(ops.A_CONTIGUOUS, h_codes, None, h_sf, wq_local.w2_codes,
+                             wq_local.w2_sf, lay)
+    else:
+        h_codes, h_scale, _, _, _ = ops.gemm1_fp8(ops.A_CONTIGUOUS, a_codes, a_scale,
+                                                  wq_local.w13_codes, wq_local.w13_scale, lay, limit)
+        y_rows = ops.gemm_fp8(ops.A_CONTIGUOUS, h_codes, h_scale, wq_local.w2_codes,
+                              wq_local.w2_scale, lay)
+    return ops.gather_rows(y_rows[:, :D] if y_rows.shape[1] != D else y_rows, lay.row_of_flat)
+
+
+def _exchange_async(rows, send_counts, recv_counts, group):
+    out = rows.new_empty((sum(recv_counts),) + tuple(rows.shape[1:]))
+    work = dist.all_to_all_single(out, rows.contiguous(), output_split_sizes=list(recv_counts),
+                                  input_split_sizes=list(send_counts), group=group, async_op=True)
+    return out, work
+
+
 def moe_forward_fp8_ep(x: torch.Tensor, wq_local: ops.Fp8ExpertWeights, weights: torch.Tensor,
                        indices: torch.Tensor, n_experts: int, limit: float,
-                       shared: torch.Tensor | None = None, group=None) -> torch.Tensor:
+                       shared: torch.Tensor | None = None, group=None,
+                       chunks: int = 1) -> torch.Tensor:
     """Expert-parallel forward of the routed experts.
 
     x [T_local, D] bf16; weights / indices [T_local, k] with GLOBAL expert ids in [0, n_experts);
     ``wq_local`` holds this rank's experts (n_experts / world of them).  Returns bf16 [T_local, D].
+    With ``chunks`` > 1 the local tokens are processed in that many slices and the all-to-alls
+    of one slice run (on NCCL's stream) while the GEMMs of the previous slice run; the per-peer
+    counts of all slices are exchanged at once, so there is still one host synchronisation.
     """
     world = dist.get_world_size(group)
     T, D = x.shape
@@ -91,35 +124,64 @@ def moe_forward_fp8_ep(x: torch.Tensor, wq_local: ops.Fp8ExpertWeights, weights:
     e_local = n_experts // world
     if wq_local.E != e_local:
         raise ops.Nv41Error(f"rank holds {wq_local.E} experts, expected {e_local}")
-    flat = indices.reshape(-1)
-    dest = torch.div(flat, e_local, rounding_mode="floor")
-    # stable sort of the rows by destination rank: the layout kernels with "expert" = rank
-    by_rank = ops.build_layout(dest, world, k)
-    plan = make_plan(by_rank.order, by_rank.counts, group)
-    # quantise once per token, before sending; pack the rows in destination order
-    x_codes, x_scale = ops.quant_fp8_1x128(x.contiguous())             # [T, Dp], [T, Dp/128]
-    src_tok = torch.div(plan.order, k, rounding_mode="floor")
-    order_l = plan.order.long()
-    send_codes = ops.gather_rows_bytes(x_codes, src_tok)
-    send_scale = x_scale.index_select(0, src_tok.long())
-    meta = torch.stack(((flat.index_select(0, order_l) % e_local).to(torch.int32),
-                        weights.reshape(-1).float().index_select(0, order_l).view(torch.int32)), 1)
-    r_codes, r_scale, r_meta = dispatch(plan, (send_codes, send_scale, meta), group)
-    # local grouped GEMMs on the received rows (each received row is its own "token", k = 1)
-    n_recv = plan.n_recv
-    if n_recv > 0:
-        lay = ops.build_layout(r_meta[:, 0].contiguous(), e_local, 1,
-                               r_meta[:, 1].contiguous().view(torch.float32))
-        h_codes, h_scale, _, _, _ = ops.gemm1_fp8(ops.A_GATHER_FP8, r_codes,
-                                                  r_scale.t().contiguous(), wq_local.w13_codes,
-                                                  wq_local.w13_scale, lay, limit)
-        y_rows = ops.gemm_fp8(ops.A_CONTIGUOUS, h_codes, h_scale, wq_local.w2_codes,
-                              wq_local.w2_scale, lay)
-        y_recv = ops.gather_rows(y_rows[:, :D] if y_rows.shape[1] != D else y_rows, lay.row_of_flat)
-    else:
-        y_recv = x.new_empty((0, D))
-    y_back = give_back(plan, y_recv, group)                            # [n_send, D] sorted order
-    return ops.combine(y_back, plan.pos_of_flat, T, k, shared)
+    chunks = max(1, min(chunks, T))
+    bounds = [T * c // chunks for c in range(chunks + 1)]
+    x = x.contiguous()
+    # 1. per slice: stable sort of the routed rows by destination rank (layout kernels with
+    #    "expert" = rank); all counts exchanged in one all-to-all and read on the host once
+    by_rank, flats = [], []
+    for c in range(chunks):
+        flat = indices[bounds[c]:bounds[c + 1]].reshape(-1)
+        flats.append(flat)
+        by_rank.append(ops.build_layout(torch.div(flat, e_local, rounding_mode="floor"), world, k))
+    send = torch.stack([b.counts for b in by_rank], 1).to(torch.int64).contiguous()   # [G, C]
+    recv = torch.empty_like(send)
+    dist.all_to_all_single(recv, send, group=group)
+    both = torch.stack((send, recv)).tolist()                  # the one host synchronisation
+    x_codes, x_scale = ops.quant_fp8_1x128(x, ue8m0=wq_local.ue8m0)    # once per token
+
+    def start_dispatch(c):
+        order = by_rank[c].order
+        tok = torch.div(order, k, rounding_mode="floor") + bounds[c]
+        order_l = order.long()
+        meta = torch.stack(
+            ((flats[c].index_select(0, order_l) % e_local).to(torch.int32),
+             weights[bounds[c]:bounds[c + 1]].reshape(-1).float().index_select(0, order_l)
+             .view(torch.int32)), 1)
+        sc = [int(both[0][g][c]) for g in range(world)]
+        rc = [int(both[1][g][c]) for g in range(world)]
+        payloads = (ops.gather_rows_bytes(x_codes, tok.int()),
+                    x_scale.index_select(0, tok.long()), meta)
+        return sc, rc, [_exchange_async(p, sc, rc, group) for p in payloads]
+
+    outs = []
+    pending = start_dispatch(0)
+    back = None
+    for c in range(chunks):
+        sc, rc, recvd = pending
+        if c + 1 < chunks:
+            pending = start_dispatch(c + 1)        # next slice's rows travel during this slice's GEMMs
+        for _, work in recvd:
+            work.wait()
+        y_recv = _local_experts(recvd[0][0], recvd[1][0], recvd[2][0], wq_local, e_local, limit, D)
+        if back is not None:                       # finish the previous slice's return trip
+            pc, y_back, work = back
+            work.wait()
+            outs.append(_combine_slice(pc, y_back, by_rank, bounds, k, shared))
+        y_back, work = _exchange_async(y_recv, rc, sc, group)
+        back = (c, y_back, work)
+    pc, y_back, work = back
+    work.wait()
+    outs.append(_combine_slice(pc, y_back, by_rank, bounds, k, shared))
+    return outs[0] if chunks == 1 else torch.cat(outs, 0)
+
+
+def _combine_slice(c, y_back, by_rank, bounds, k, shared):
+    order = by_rank[c].order
+    pos = torch.empty_like(order)
+    pos[order.long()] = torch.arange(order.numel(), dtype=order.dtype, device=order.device)
+    sh = None if shared is None else shared[bounds[c]:bounds[c + 1]]
+    return ops.combine(y_back, pos, bounds[c + 1] - bounds[c], k, sh)
 
 
 def shard_expert_weights(w1, w3, w2, rank: int, world: int):

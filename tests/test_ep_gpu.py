@@ -37,7 +37,10 @@ def _worker(rank, world, port):
         shared = torch.randn(T, CASE["D"], device="cuda").bfloat16()
         out = ep.moe_forward_fp8_ep(g["x"][sl], wq_local, g["weights"][sl], g["indices"][sl],
                                     CASE["E"], 10.0, shared)
+        out3 = ep.moe_forward_fp8_ep(g["x"][sl], wq_local, g["weights"][sl], g["indices"][sl],
+                                     CASE["E"], 10.0, shared, chunks=3)
         ops.check_status()
+        assert torch.equal(out, out3)
         wq_all = ops.quantize_expert_weights(g["w1"], g["w3"], g["w2"])
         single = ops.moe_forward_fp8(g["x"][sl], wq_all, g["weights"][sl], g["indices"][sl], 10.0,
                                      shared)
