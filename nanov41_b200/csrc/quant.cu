@@ -52,47 +52,104 @@ __device__ __forceinline__ uint32_t fp8x4_codes(float a, float b, float c, float
 }
 
 // ------------------------------------------------------------------------- FP8 1x128 rows
-// One half-warp (16 lanes x 8 elements) per 1x128 block.  Work item = (row, k-block),
-// k-block fastest.  `gather` (optional) maps output row -> source row (-1 = all-zero row).
+// One quarter-warp (8 lanes x 16 elements) per 1x128 block: lane l holds elements [8l, 8l+8)
+// and [64+8l, 64+8l+8), so both loads of a quarter-warp are one contiguous 128-byte run.  The
+// launch makes the number of quarter-warps a multiple of the k-blocks per row, so a quarter-warp
+// keeps its k-block and walks down the rows: no division and no 64-bit index arithmetic beyond
+// pointer steps inside the loop.  Two rows per trip, all four loads issued first.
+// The block maximum is taken on the bf16 bit patterns (two per word, unsigned 16-bit max after
+// clearing the signs): for non-negative floats the bit order is the value order, and any inf /
+// NaN element shows as a pattern >= 0x7F80, which selects the IEEE-division path below.
+// `gather` (optional) maps output row -> source row (-1 = all-zero row).
+struct Chunk16 { uint4 a, b; };
+
+__device__ __forceinline__ uint32_t absmax_bf16x16(const Chunk16& c) {
+  const uint32_t M = 0x7FFF7FFFu;
+  uint32_t m = __vmaxu2(c.a.x & M, c.a.y & M);
+  m = __vmaxu2(m, __vmaxu2(c.a.z & M, c.a.w & M));
+  m = __vmaxu2(m, __vmaxu2(c.b.x & M, c.b.y & M));
+  m = __vmaxu2(m, __vmaxu2(c.b.z & M, c.b.w & M));
+  return max(m & 0xFFFFu, m >> 16);
+}
+
+template <bool kUe8m0>
+__device__ __forceinline__ void quant_1x128_chunk(const Chunk16& c, unsigned qmask, int sub,
+                                                  uint8_t* __restrict__ code_dst,
+                                                  float* __restrict__ scale_dst) {
+  uint32_t m = absmax_bf16x16(c);
+#pragma unroll
+  for (int o = 4; o >= 1; o >>= 1) m = max(m, __shfl_xor_sync(qmask, m, o));
+  uint2 lo, hi;
+  float s;
+  if (m >= 0x7F80u) {   // some inf / NaN in the block (uniform over the quarter-warp)
+    float f[8], g[8];
+    unpack_bf16x8(c.a, f);
+    unpack_bf16x8(c.b, g);
+    float amax = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fmaxf(fabsf(f[i]), fabsf(g[i])));
+#pragma unroll
+    for (int o = 4; o >= 1; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(qmask, amax, o));
+    s = block_scale(amax, kUe8m0);
+    const float r = __frcp_rn(s);
+    lo.x = fp8x4_codes(f[0], f[1], f[2], f[3], s, r);
+    lo.y = fp8x4_codes(f[4], f[5], f[6], f[7], s, r);
+    hi.x = fp8x4_codes(g[0], g[1], g[2], g[3], s, r);
+    hi.y = fp8x4_codes(g[4], g[5], g[6], g[7], s, r);
+  } else {
+    s = block_scale(__uint_as_float(m << 16), kUe8m0);
+    const float r = __frcp_rn(s);
+    const uint64_t ns2 = f32x2_pack(-s, -s), r2 = f32x2_pack(r, r);
+    lo = e4m3x8_div_bf16(c.a, ns2, r2);
+    hi = e4m3x8_div_bf16(c.b, ns2, r2);
+  }
+  *reinterpret_cast<uint2*>(code_dst) = lo;
+  *reinterpret_cast<uint2*>(code_dst + 64) = hi;
+  if (sub == 0) *scale_dst = s;
+}
+
+template <bool kGather, bool kUe8m0>
 __global__ void __launch_bounds__(256)
 quant_fp8_1x128_kernel(const __nv_bfloat16* __restrict__ x, long long ld_x,
                        const int* __restrict__ gather, uint8_t* __restrict__ codes,
                        float* __restrict__ scales, long long ss_row, long long ss_kb,
-                       long long rows, int K, int Kpad, int ue8m0) {
+                       long long rows, int K, int Kpad) {
   const int nkb = Kpad / 128;
-  const long long n_items = rows * nkb;
   const int lane = threadIdx.x & 31;
-  const int sub = lane & 15;            // position inside the block: elements [sub*8, sub*8+8)
-  const long long half_id =
-      (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 4;
-  const long long n_halves = (static_cast<long long>(gridDim.x) * blockDim.x) >> 4;
-  const unsigned hmask = 0xFFFFu << (lane & 16);   // shuffles stay inside the half-warp
-  for (long long item = half_id; item < n_items; item += n_halves) {
-    const long long row = item / nkb;
-    const int kb = static_cast<int>(item - row * nkb);
-    float f[8];
-#pragma unroll
-    for (int i = 0; i < 8; ++i) f[i] = 0.f;
-    {
-      const int col = kb * 128 + sub * 8;
-      const long long src = gather ? static_cast<long long>(gather[row]) : row;
-      if (src >= 0 && col < K) {  // K % 8 == 0, so a chunk is entirely inside or outside
-        const uint4 v = __ldg(reinterpret_cast<const uint4*>(x + src * ld_x + col));
-        unpack_bf16x8(v, f);
-      }
+  const int sub = lane & 7;
+  const unsigned qmask = 0xFFu << (lane & 24);      // shuffles stay inside the quarter-warp
+  const unsigned q_id = (blockIdx.x * blockDim.x + threadIdx.x) >> 3;
+  const unsigned n_q = (gridDim.x * blockDim.x) >> 3;   // a multiple of nkb (see the launch)
+  const int kb = static_cast<int>(q_id % nkb);
+  const long long row0 = q_id / nkb;
+  const long long drow = n_q / nkb;
+  const int col = kb * 128 + sub * 8;
+  const bool in_a = col < K, in_b = col + 64 < K;   // K % 8 == 0: a chunk is all in or all out
+  const __nv_bfloat16* xp = x + col;
+  uint8_t* cp = codes + row0 * Kpad + col;
+  float* sp = scales + row0 * ss_row + kb * ss_kb;
+  const long long c_step = drow * Kpad, s_step = drow * ss_row;
+  auto load = [&](long long row) {
+    Chunk16 c;
+    c.a = make_uint4(0u, 0u, 0u, 0u);
+    c.b = c.a;
+    const long long src = kGather ? static_cast<long long>(__ldg(gather + row)) : row;
+    if (!kGather || src >= 0) {
+      const __nv_bfloat16* p = xp + src * ld_x;
+      if (in_a) c.a = __ldg(reinterpret_cast<const uint4*>(p));
+      if (in_b) c.b = __ldg(reinterpret_cast<const uint4*>(p + 64));
     }
-    float amax = 0.f;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(f[i]));
-#pragma unroll
-    for (int o = 8; o >= 1; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(hmask, amax, o));
-    const float s = block_scale(amax, ue8m0);
-    const float r = __frcp_rn(s);
-    uint2 out;
-    out.x = fp8x4_codes(f[0], f[1], f[2], f[3], s, r);
-    out.y = fp8x4_codes(f[4], f[5], f[6], f[7], s, r);
-    *reinterpret_cast<uint2*>(codes + row * Kpad + kb * 128 + sub * 8) = out;
-    if (sub == 0) scales[row * ss_row + kb * ss_kb] = s;
+    return c;
+  };
+  for (long long row = row0; row < rows; row += 2 * drow) {
+    const bool two = row + drow < rows;             // uniform over the quarter-warp
+    const Chunk16 c0 = load(row);
+    Chunk16 c1;
+    if (two) c1 = load(row + drow);
+    quant_1x128_chunk<kUe8m0>(c0, qmask, sub, cp, sp);
+    if (two) quant_1x128_chunk<kUe8m0>(c1, qmask, sub, cp + c_step, sp + s_step);
+    cp += 2 * c_step;
+    sp += 2 * s_step;
   }
 }
 
@@ -401,15 +458,19 @@ extern "C" int nv41_quant_fp8_1x128(const void* x_bf16, long long ld_x, const in
   if (!x_bf16 || !codes || !scales || rows < 0 || K <= 0 || (K % 8) != 0 || ld_x < K)
     return NV41_ERR_INVALID;
   const int Kpad = (K + 127) / 128 * 128;
-  const long long items = rows * (Kpad / 128);
-  long long blocks = (items * 16 + 255) / 256;
-  const long long cap = 148LL * 8 * 4;
+  const int nkb = Kpad / 128;
+  const long long items = rows * nkb;               // one quarter-warp (8 threads) per item
+  long long blocks = (items * 8 + 255) / 256;
+  const long long cap = 148LL * 8 * 2;
   if (blocks > cap) blocks = cap;
-  quant_fp8_1x128_kernel<<<static_cast<unsigned>(blocks), 256, 0,
-                           static_cast<cudaStream_t>(stream)>>>(
+  blocks = (blocks + nkb - 1) / nkb * nkb;          // quarter-warps a multiple of k-blocks per row
+  auto* kern = gather_rows ? (ue8m0 ? quant_fp8_1x128_kernel<true, true>
+                                    : quant_fp8_1x128_kernel<true, false>)
+                           : (ue8m0 ? quant_fp8_1x128_kernel<false, true>
+                                    : quant_fp8_1x128_kernel<false, false>);
+  kern<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(x_bf16), ld_x, gather_rows,
-      static_cast<uint8_t*>(codes), scales, scale_stride_row, scale_stride_kb, rows, K, Kpad,
-      ue8m0);
+      static_cast<uint8_t*>(codes), scales, scale_stride_row, scale_stride_kb, rows, K, Kpad);
   return launch_status();
 }
 

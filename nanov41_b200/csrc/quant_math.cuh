@@ -30,4 +30,53 @@ __device__ __forceinline__ uint32_t e4m3x4_div(float a, float b, float c, float 
   return lo | (hi << 16);
 }
 
+// ---- packed (two floats per instruction) form of the same division, for finite operands
+__device__ __forceinline__ uint64_t f32x2_pack(float lo, float hi) {
+  uint64_t v;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(v) : "f"(lo), "f"(hi));
+  return v;
+}
+__device__ __forceinline__ float2 f32x2_unpack(uint64_t v) {
+  float2 f;
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(f.x), "=f"(f.y) : "l"(v));
+  return f;
+}
+__device__ __forceinline__ uint64_t f32x2_mul(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ uint64_t f32x2_fma(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+
+// e4m3 codes of eight FINITE values given as four words of two bf16 each (element 2i in the low
+// half), divided by the block scale s (ns2 = {-s, -s}, r2 = {RN(1/s), RN(1/s)}).  Same
+// arithmetic as div_by_scale per lane: |x / s| <= 448 (1 + eps) by construction of s, so the
+// saturating conversion needs no clamp first; the sign of a -0.0 input, which the correction
+// steps lose, is put back from the input's sign bits.
+__device__ __forceinline__ uint2 e4m3x8_div_bf16(const uint4& v, uint64_t ns2, uint64_t r2) {
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+  uint32_t c16[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const uint64_t a = f32x2_pack(__uint_as_float(w[i] << 16), __uint_as_float(w[i] & 0xFFFF0000u));
+    uint64_t q = f32x2_mul(a, r2);
+    uint64_t e = f32x2_fma(ns2, q, a);
+    q = f32x2_fma(e, r2, q);
+    e = f32x2_fma(ns2, q, a);
+    q = f32x2_fma(e, r2, q);
+    c16[i] = __nv_cvt_float2_to_fp8x2(f32x2_unpack(q), __NV_SATFINITE, __NV_E4M3);
+  }
+  uint2 out;
+  out.x = c16[0] | (c16[1] << 16);
+  out.y = c16[2] | (c16[3] << 16);
+  // bytes 1,3 of each word hold the bf16 sign bits: replicate them (prmt sign mode), keep bit 7
+  out.x |= __byte_perm(w[0], w[1], 0xFDB9) & 0x80808080u;
+  out.y |= __byte_perm(w[2], w[3], 0xFDB9) & 0x80808080u;
+  return out;
+}
+
 }  // namespace nv41

@@ -1,9 +1,11 @@
-"""Small fixed workload for profiler captures: a few launches of every kernel of the FP8 forward.
+"""Small fixed workload for profiler captures: one launch of every kernel family of the path.
 
-    python -m nanov41_b200.profile_case [--tokens 4096] [--experts 16] [--iters 2]
+    python -m nanov41_b200.profile_case [--tokens 4096] [--experts 16]
 
 Shapes follow BASELINE config 2 (k=6, D=I=1024) at a size whose buffers stay far below a GB, so
-an `ncu --set full` capture of one kernel ends by itself in about a minute.
+an `ncu --set full` capture of a few kernels ends by itself in a minute or two.  Order of the
+launches: activation quantizer on a 128 MiB bf16 matrix (larger than L2, for DRAM figures), then
+the FP8 forward with fp32 scales, with ue8m0 scales, and the NVFP4 forward.
 """
 from __future__ import annotations
 
@@ -19,15 +21,20 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--tokens", type=int, default=4096)
     ap.add_argument("--experts", type=int, default=16)
-    ap.add_argument("--iters", type=int, default=2)
     args = ap.parse_args()
+    big = torch.randn(32768, 2048, device="cuda").bfloat16()
+    ops.quant_fp8_1x128(big)
+    del big
     c = make_case(T=args.tokens, E=args.experts, k=6, D=1024, I=1024, seed=1)
     g = {n: t.cuda() for n, t in c.items()}
-    wq = ops.quantize_expert_weights(g["w1"], g["w3"], g["w2"])
-    for _ in range(args.iters):
-        out = ops.moe_forward_fp8(g["x"], wq, g["weights"], g["indices"], 10.0)
+    acc = 0.0
+    for ue8m0 in (False, True):
+        wq = ops.quantize_expert_weights(g["w1"], g["w3"], g["w2"], ue8m0=ue8m0)
+        acc += float(ops.moe_forward_fp8(g["x"], wq, g["weights"], g["indices"], 10.0).float().abs().mean())
+    w4 = ops.quantize_expert_weights_nvfp4(g["w1"], g["w3"], g["w2"])
+    acc += float(ops.moe_forward_nvfp4(g["x"], w4, g["weights"], g["indices"], 10.0).float().abs().mean())
     ops.check_status()
-    print("profile_case ok", float(out.float().abs().mean()))
+    print("profile_case ok", acc)
 
 
 if __name__ == "__main__":
