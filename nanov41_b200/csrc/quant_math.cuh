@@ -3,6 +3,8 @@
 #include <cuda_fp8.h>
 #include <cstdint>
 
+#include "f32x2.cuh"
+
 namespace nv41 {
 
 // Correctly rounded a / s given r = RN(1 / s): a product and two FMA correction steps.  Exact for
@@ -31,27 +33,6 @@ __device__ __forceinline__ uint32_t e4m3x4_div(float a, float b, float c, float 
 }
 
 // ---- packed (two floats per instruction) form of the same division, for finite operands
-__device__ __forceinline__ uint64_t f32x2_pack(float lo, float hi) {
-  uint64_t v;
-  asm("mov.b64 %0, {%1, %2};" : "=l"(v) : "f"(lo), "f"(hi));
-  return v;
-}
-__device__ __forceinline__ float2 f32x2_unpack(uint64_t v) {
-  float2 f;
-  asm("mov.b64 {%0, %1}, %2;" : "=f"(f.x), "=f"(f.y) : "l"(v));
-  return f;
-}
-__device__ __forceinline__ uint64_t f32x2_mul(uint64_t a, uint64_t b) {
-  uint64_t d;
-  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
-  return d;
-}
-__device__ __forceinline__ uint64_t f32x2_fma(uint64_t a, uint64_t b, uint64_t c) {
-  uint64_t d;
-  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
-  return d;
-}
-
 // e4m3 codes of eight FINITE values given as four words of two bf16 each (element 2i in the low
 // half), divided by the block scale s (ns2 = {-s, -s}, r2 = {RN(1/s), RN(1/s)}).  Same
 // arithmetic as div_by_scale per lane: |x / s| <= 448 (1 + eps) by construction of s, so the
