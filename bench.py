@@ -176,15 +176,27 @@ def run_ep(args, world, rank, local, dev):
     w_host = weights.cpu().pin_memory()
     out_host = torch.empty((T, D), dtype=torch.bfloat16).pin_memory()
 
+    ctx = ep.PeerContext(T, k, D) if args.ep_mode == "peer" else None
+    seg = (ep.SegContext(T, k, E, D, ue8m0=args.scale_fmt == "ue8m0")
+           if args.ep_mode == "segments" else None)
+
+    def forward(xd, wd, idd):
+        if seg is not None:
+            return ep.moe_forward_fp8_seg(seg, xd, wq, wd, idd, E, LIMIT,
+                                          slice_rows=args.ep_slice_rows)
+        if ctx is not None:
+            return ep.moe_forward_fp8_peer(ctx, xd, wq, wd, idd, E, LIMIT, slices=args.ep_slices,
+                                           copy_sms=args.ep_copy_sms)
+        return ep.moe_forward_fp8_ep(xd, wq, wd, idd, E, LIMIT, chunks=args.ep_chunks)
+
     def step_device():
-        return ep.moe_forward_fp8_ep(x, wq, weights, indices, E, LIMIT, chunks=args.ep_chunks)
+        return forward(x, weights, indices)
 
     def step_e2e():
         xd = x_host.to(dev, non_blocking=True)
         idd = idx_host.to(dev, non_blocking=True)
         wd = w_host.to(dev, non_blocking=True)
-        out_host.copy_(ep.moe_forward_fp8_ep(xd, wq, wd, idd, E, LIMIT, chunks=args.ep_chunks),
-                       non_blocking=True)
+        out_host.copy_(forward(xd, wd, idd), non_blocking=True)
 
     def timed(fn, steps, warmup):
         for _ in range(warmup):
@@ -262,7 +274,8 @@ def run_ep(args, world, rank, local, dev):
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_dev,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "fp8_e4m3 (fp32 accumulate, bf16 out)", "data": "synthetic",
-            "config": dict(c5_config(world), ep_chunks=args.ep_chunks), "scale_fmt": args.scale_fmt,
+            "config": dict(c5_config(world), ep_chunks=args.ep_chunks, ep_mode=args.ep_mode, ep_slices=args.ep_slices,
+                           ep_copy_sms=args.ep_copy_sms), "scale_fmt": args.scale_fmt,
             "e2e": {"value": flops / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s",
                     "ms_per_step": ms_e2e,
                     "h2d_bytes_per_step": x_host.numel() * 2 + idx_host.numel() * 8 + w_host.numel() * 4,
@@ -538,6 +551,15 @@ def main():
     ap.add_argument("--cpu-sample-tokens", type=int, default=16384)
     ap.add_argument("--ep-chunks", type=int, default=1,
                     help="N > 1: token slices whose all-to-alls overlap the previous slice's GEMMs")
+    ap.add_argument("--ep-mode", default="nccl", choices=["nccl", "peer", "segments"],
+                    help="N > 1: rows travel through NCCL all-to-alls, or are pulled from / pushed to "
+                         "peer-mapped memory by the owner's own kernels")
+    ap.add_argument("--ep-slice-rows", type=int, default=65536,
+                    help="segments mode: rows per copy / GEMM slice of a peer's run")
+    ap.add_argument("--ep-slices", type=int, default=1,
+                    help="peer mode: runs of the owner's row space whose pull / push overlap the GEMMs")
+    ap.add_argument("--ep-copy-sms", type=int, default=0,
+                    help="peer mode with slices: SMs the GEMM grids leave to the pull / push kernels")
     ap.add_argument("--workload", default="c2", choices=["c2", "d8", "d12"],
                     help="c2 = BASELINE config 2 (headline); d8 / d12 = expert stacks of configs 3 / 4")
     ap.add_argument("--scale-fmt", default="fp32", choices=["fp32", "ue8m0"],

@@ -247,6 +247,65 @@ int nv41_swiglu_bwd_quant(const void* dact, const void* gate, const void* up,
 int nv41_moe_wgrad_bf16(const void* a_rows, const void* b_rows, const int* pad_off, int E, int M,
                         int N, long long P_max, void* out, unsigned* status, void* stream);
 
+/* ---- expert parallelism over peer-mapped memory ---------------------------------------------
+ * No reference counterpart: the reference shards experts only through replicated tokens and an
+ * fp32 all_reduce of the layer output (nanov41/fast_moe.py:446-450,468-471;
+ * nanov41/_ref_patched_model.py:880-887,918-919).  Here the owner of an expert reads routed rows
+ * from, and writes finished rows to, buffers of the other ranks of the node mapped with CUDA IPC.
+ * The kernels below hold no waits; the caller orders them between ranks with collectives. */
+#define NV41_EP_MAX_RANKS 8
+#define NV41_PEER_HANDLE_BYTES 64
+
+/* Device buffer that other processes of the node may map (plain cudaMalloc) / release it. */
+int nv41_peer_alloc(unsigned long long bytes, void** dev_ptr);
+int nv41_peer_free(void* dev_ptr);
+/* 64-byte handle of a buffer from nv41_peer_alloc, to be sent to the peers by any means. */
+int nv41_peer_export(const void* dev_ptr, unsigned char* handle64);
+/* Map / unmap a peer's buffer in this process (enables peer access to its device). */
+int nv41_peer_open(const unsigned char* handle64, void** dev_ptr);
+int nv41_peer_close(void* dev_ptr);
+
+/* Copy `height` runs of `width_bytes` between device buffers of this process or mapped peers
+ * (pitches in bytes) with the copy engines: no SM is used, so the copy runs beside the GEMMs. */
+int nv41_peer_copy_2d(void* dst, unsigned long long dst_pitch, const void* src,
+                      unsigned long long src_pitch, unsigned long long width_bytes,
+                      unsigned long long height, void* stream);
+
+/* Pull the FP8 rows routed to this rank out of the home ranks' buffers into the padded
+ * expert-major operand (the permute of nanov41/fast_moe.py:399 done across ranks):
+ * row p with arrival index a = row_token[p] >= 0, a in [arrival_offsets[g], arrival_offsets[g+1]),
+ * copies codes peer_codes[g][desc[a].token] (u8, row stride src_ld) and the K/128 scales
+ * peer_scales[g][desc[a].token][:] (fp32, row-major); padding rows get zero codes, scale 1.
+ * peer_codes / peer_scales / arrival_offsets are HOST arrays ([n_ranks], [n_ranks], [n_ranks+1]);
+ * desc: device int32 [n_arrived][4] = {local expert, weight bits, home token, flat (token,slot)
+ * index}.  Only padded rows [row_begin, row_end) are filled (slices of the row space can be
+ * pulled on one stream while the GEMMs of earlier slices run on another).  Outputs as
+ * nv41_gather_fp8_rows, indexed by the absolute padded row.  copy_ctas: 0 = a wide grid of
+ * plain loads / stores; n > 0 = n CTAs of bulk-copy (TMA) movers that each occupy a whole SM, to
+ * run beside a GEMM limited with nv41_set_gemm_cta_limit (needs K % 512 == 0; their bounded
+ * waits report through `status`, which may be null). */
+int nv41_ep_pull_fp8_rows(const void* const* peer_codes, const void* const* peer_scales,
+                          int n_ranks, const int* arrival_offsets, const int* desc,
+                          const int* row_token, const int* meta, int K, long long src_ld,
+                          long long P_max, long long row_begin, long long row_end,
+                          void* codes_rows, float* scales_rows_kmajor, void* sf_atoms,
+                          int copy_ctas, unsigned* status, void* stream);
+
+/* Push finished bf16 rows to their home ranks: peer_out[g][desc[a].flat][0:D] =
+ * y_rows[p - row_begin] for every routed padded row p in [row_begin, row_end) (the un-permute of
+ * nanov41/fast_moe.py:311-338 done across ranks; the home rank then sums its k rows per token
+ * with nv41_moe_combine).  row_token / desc are indexed by the absolute padded row. */
+int nv41_ep_push_rows_bf16(const void* y_rows, long long ld_y, const int* row_token,
+                           const int* meta, const int* desc, const int* arrival_offsets,
+                           void* const* peer_out, int n_ranks, long long row_begin,
+                           long long row_end, int D, int copy_ctas, unsigned* status,
+                           void* stream);
+
+/* Upper bound on the CTAs of the persistent grouped GEMMs of this library (0 = one per SM, the
+ * default).  A smaller grid leaves SMs free for copy kernels that run beside the GEMMs on other
+ * streams.  Process-wide; no reference counterpart. */
+int nv41_set_gemm_cta_limit(int max_ctas);
+
 #ifdef __cplusplus
 }
 #endif

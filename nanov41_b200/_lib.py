@@ -47,6 +47,17 @@ SIGNATURES = {
     "nv41_gather_rows_bf16": (_i, [_p, _ll, _p, _ll, _i, _p, _p]),
     "nv41_swiglu_bwd_quant": (_i, [_p, _p, _p, _p, _p, _i, _ll, _f, _p, _p, _p, _p, _p, _i, _p]),
     "nv41_moe_wgrad_bf16": (_i, [_p, _p, _p, _i, _i, _i, _ll, _p, _p, _p]),
+    "nv41_peer_alloc": (_i, [C.c_ulonglong, _p]),
+    "nv41_peer_free": (_i, [_p]),
+    "nv41_peer_export": (_i, [_p, _p]),
+    "nv41_peer_open": (_i, [_p, _p]),
+    "nv41_peer_close": (_i, [_p]),
+    "nv41_peer_copy_2d": (_i, [_p, C.c_ulonglong, _p, C.c_ulonglong, C.c_ulonglong, C.c_ulonglong,
+                               _p]),
+    "nv41_ep_pull_fp8_rows": (_i, [_p, _p, _i, _p, _p, _p, _p, _i, _ll, _ll, _ll, _ll, _p, _p, _p,
+                                   _i, _p, _p]),
+    "nv41_ep_push_rows_bf16": (_i, [_p, _ll, _p, _p, _p, _p, _p, _i, _ll, _ll, _i, _i, _p, _p]),
+    "nv41_set_gemm_cta_limit": (_i, [_i]),
 }
 
 _lib = None

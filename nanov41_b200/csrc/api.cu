@@ -3,7 +3,22 @@
 
 #include "../../include/nanov41_b200.h"
 
-extern "C" int nv41_abi_version(void) { return 100; }
+#include <atomic>
+
+#include "util.cuh"
+
+namespace nv41 {
+static std::atomic<int> g_gemm_cta_limit{0};
+int gemm_cta_limit() { return g_gemm_cta_limit.load(std::memory_order_relaxed); }
+}  // namespace nv41
+
+extern "C" int nv41_abi_version(void) { return 101; }
+
+extern "C" int nv41_set_gemm_cta_limit(int max_ctas) {
+  if (max_ctas < 0) return NV41_ERR_INVALID;
+  nv41::g_gemm_cta_limit.store(max_ctas, std::memory_order_relaxed);
+  return NV41_OK;
+}
 
 extern "C" int nv41_status_read(const unsigned* status, unsigned* raw_host, void* stream) {
   if (!status) return NV41_ERR_INVALID;

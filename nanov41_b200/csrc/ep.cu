@@ -1,0 +1,513 @@
+// Expert parallelism over peer-mapped HBM (NVLink / NVSwitch), single node, up to 8 ranks.
+//
+// Each rank keeps three buffers that its peers map through CUDA IPC: the FP8 codes and 1x128
+// scales of its own tokens, quantised once per step, and the landing zone of the expert outputs
+// of its (token, slot) rows.  The owner of an expert then
+//   * PULLS the rows routed to it straight from the home ranks' buffers into its padded
+//     expert-major operand (plain loads from peer memory, one warp per row), and
+//   * PUSHES every finished output row to its home rank's landing zone at the row's flat
+//     (token, slot) index (plain stores to peer memory),
+// so a routed row crosses NVLink once each way and no pack / unpack copy exists on either side.
+// Only the 16-byte per-row descriptors (local expert, router weight, home token, flat index)
+// travel through NCCL; that all-to-all also orders "peer has quantised" before "owner pulls".
+//
+// The kernels contain no waits: ordering between ranks comes from the stream order of the
+// collectives around them (see nanov41_b200/ep.py).
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <cstdint>
+#include <cstring>
+
+#include "../../include/nanov41_b200.h"
+#include "ptx.cuh"
+#include "util.cuh"
+
+namespace nv41 {
+
+constexpr int kMaxRanks = NV41_EP_MAX_RANKS;
+
+struct PeerTable {
+  const void* a[kMaxRanks];   // per rank: FP8 codes   | output landing zone
+  const void* b[kMaxRanks];   // per rank: 1x128 scales | unused
+  int off[kMaxRanks + 1];     // arrival index range [off[g], off[g+1]) came from rank g
+  int n;
+};
+
+__device__ __forceinline__ int rank_of(const PeerTable& t, int arrival) {
+  int g = 0;
+#pragma unroll
+  for (int i = 1; i < kMaxRanks; ++i) g += (i < t.n && arrival >= t.off[i]) ? 1 : 0;
+  return g;
+}
+
+// Copy `chunks` 16-byte pieces of U rows at once (a null source reads as zeros, a null
+// destination is skipped): every lane has 2 U loads in flight before the first store, which is
+// what keeps a remote read stream busy from few SMs.
+template <int U>
+__device__ __forceinline__ void copy_rows(const uint4* const (&src)[U], uint4* const (&dst)[U],
+                                          int chunks, int lane) {
+  for (int c0 = 0; c0 < chunks; c0 += 64) {
+    uint4 v[U][2];
+#pragma unroll
+    for (int u = 0; u < U; ++u)
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        const int c = c0 + j * 32 + lane;
+        v[u][j] = make_uint4(0u, 0u, 0u, 0u);
+        if (src[u] && c < chunks) v[u][j] = src[u][c];
+      }
+#pragma unroll
+    for (int u = 0; u < U; ++u)
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        const int c = c0 + j * 32 + lane;
+        if (dst[u] && c < chunks) dst[u][c] = v[u][j];
+      }
+  }
+}
+
+constexpr int kRowsPerWarp = 4;
+
+// a_codes[p] = codes_{g}[token], scales_rows[kb][p] = scales_{g}[token][kb] for the padded row
+// p whose arrival index row_token[p] belongs to rank g; padding rows get zero codes, scale 1.
+// desc[arrival] = {local expert, weight bits, home token, flat index}.  A warp takes four rows
+// per trip.
+__global__ void __launch_bounds__(256)
+ep_pull_fp8_rows_kernel(PeerTable t, const int4* __restrict__ desc,
+                        const int* __restrict__ row_token, const int* __restrict__ meta, int K,
+                        long long src_ld, uint8_t* __restrict__ codes_rows,
+                        float* __restrict__ scales_rows, long long P_max,
+                        uint8_t* __restrict__ atoms, long long row_begin, long long row_end) {
+  constexpr int U = kRowsPerWarp;
+  const int lane = threadIdx.x & 31;
+  const long long warp0 = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const long long nwarps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
+  const long long used = min(static_cast<long long>(meta[1]), row_end);
+  const int nkb = K / 128, chunks = K / 16;
+  for (long long p0 = row_begin + warp0 * U; p0 < used; p0 += nwarps * U) {
+    const uint4* src[U];
+    uint4* dst[U];
+    const float* src_scales[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long p = p0 + u;
+      src[u] = nullptr;
+      dst[u] = nullptr;
+      src_scales[u] = nullptr;
+      if (p >= used) continue;
+      dst[u] = reinterpret_cast<uint4*>(codes_rows + p * K);
+      const int arr = row_token[p];
+      if (arr < 0) continue;
+      const int g = rank_of(t, arr);
+      const long long tok = desc[arr].z;
+      src[u] = reinterpret_cast<const uint4*>(static_cast<const uint8_t*>(t.a[g]) + tok * src_ld);
+      src_scales[u] = static_cast<const float*>(t.b[g]) + tok * nkb;
+    }
+    copy_rows<U>(src, dst, chunks, lane);
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long p = p0 + u;
+      if (p >= used) continue;
+      for (int kb = lane; kb < nkb; kb += 32) {
+        const float s = src_scales[u] ? src_scales[u][kb] : 1.0f;
+        scales_rows[kb * P_max + p] = s;
+        if (atoms) {
+          const uint32_t byte = (__float_as_uint(s) >> 23) & 0xFFu;
+          const int r = static_cast<int>(p & 127);
+          *reinterpret_cast<uint32_t*>(atoms + ((p >> 7) * nkb + kb) * 512 + (r & 31) * 16 +
+                                       (r >> 5) * 4) = byte * 0x01010101u;
+        }
+      }
+    }
+  }
+}
+
+// out_{g}[flat] = y_rows[p - row_begin] for every padded row p in [row_begin, row_end) that holds
+// a routed row (bf16, D % 8 == 0).
+__global__ void __launch_bounds__(256)
+ep_push_rows_kernel(PeerTable t, const int4* __restrict__ desc, const int* __restrict__ row_token,
+                    const int* __restrict__ meta, const __nv_bfloat16* __restrict__ y_rows,
+                    long long ld_y, int D, long long row_begin, long long row_end) {
+  constexpr int U = kRowsPerWarp;
+  const int lane = threadIdx.x & 31;
+  const long long warp0 = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const long long nwarps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
+  const long long used = min(static_cast<long long>(meta[1]), row_end);
+  const int chunks = D / 8;
+  for (long long p0 = row_begin + warp0 * U; p0 < used; p0 += nwarps * U) {
+    const uint4* src[U];
+    uint4* dst[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long p = p0 + u;
+      src[u] = nullptr;
+      dst[u] = nullptr;
+      if (p >= used) continue;
+      const int arr = row_token[p];
+      if (arr < 0) continue;
+      const int g = rank_of(t, arr);
+      const long long flat = desc[arr].w;
+      src[u] = reinterpret_cast<const uint4*>(y_rows + (p - row_begin) * ld_y);
+      dst[u] = reinterpret_cast<uint4*>(
+          static_cast<__nv_bfloat16*>(const_cast<void*>(t.a[g])) + flat * D);
+    }
+    copy_rows<U>(src, dst, chunks, lane);
+  }
+}
+
+// ------------------------------------------------------------------ bulk-copy (TMA) movers
+// The same two copies for running BESIDE the grouped GEMMs on a few SMs.  A warp is a "mover":
+// its lane 0 keeps a ring of row-sized shared-memory slots busy with cp.async.bulk loads
+// (global or peer -> shared, completion on an mbarrier) and cp.async.bulk stores (shared ->
+// global or peer), so one SM holds >100 KB of copies in flight with eight issuing threads, where
+// plain loads would need every warp of many SMs.  The CTA's shared-memory footprint also keeps a
+// GEMM CTA off its SM, so `grid` movers' CTAs take exactly `grid` SMs.
+// Every wait is bounded; on a time-out the mover records it, waits (bounded) for the loads it
+// still has in flight and for its stores, and returns.
+constexpr int kMoversPerCta = 8;
+constexpr int kMaxRing = 8;
+constexpr int kMoverSmemBudget = 200 * 1024;
+
+__device__ __forceinline__ void bulk_load(void* smem_dst, const void* gsrc, uint32_t bytes,
+                                          uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+      ::"r"(smem_u32(smem_dst)), "l"(gsrc), "r"(bytes), "r"(smem_u32(bar))
+      : "memory");
+}
+__device__ __forceinline__ void bulk_store(void* gdst, const void* smem_src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gdst),
+               "r"(smem_u32(smem_src)), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit() {
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+template <int N>
+__device__ __forceinline__ void bulk_wait_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void bulk_wait_all() {
+  asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+}
+
+struct MoverArgs {
+  PeerTable t;
+  const int4* desc;
+  const int* row_token;
+  const int* meta;
+  long long row_begin, row_end;
+  // pull: K code bytes + nkb scale floats per row from the peers -> codes_rows / scales_rows
+  // push: row_bytes of y_rows -> peers' landing zones
+  int row_bytes, nkb;
+  long long src_ld;            // pull: source row stride (bytes); push: y_rows row stride (bytes)
+  const uint8_t* y_rows;
+  uint8_t* codes_rows;
+  float* scales_rows;
+  long long P_max;
+  uint8_t* atoms;
+  int ring, slot_bytes;
+  unsigned* status;
+};
+
+template <bool kPull>
+__global__ void __launch_bounds__(kMoversPerCta * 32) ep_mover_kernel(MoverArgs g) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem);                 // [movers][kMaxRing]
+  volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(smem + 512);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  uint64_t* bar = bars + warp * kMaxRing;
+  uint8_t* slots = smem + 1024 + static_cast<size_t>(warp) * g.ring * g.slot_bytes;
+  if (threadIdx.x == 0) *abort_flag = 0u;
+  if (lane == 0) {
+    for (int s = 0; s < g.ring; ++s) mbar_init(bar + s, 1u);
+    fence_mbar_init();
+  }
+  __syncthreads();
+  const long long mover = static_cast<long long>(blockIdx.x) * kMoversPerCta + warp;
+  const long long n_movers = static_cast<long long>(gridDim.x) * kMoversPerCta;
+  const long long used = min(static_cast<long long>(g.meta[1]), g.row_end);
+  const long long first = g.row_begin + mover;
+  const long long n = first < used ? (used - first + n_movers - 1) / n_movers : 0;
+  const int depth = g.ring - 2;          // loads in flight; two slots are being stored from
+
+  // Row descriptors are fetched 32 rows at a time, one row per lane, a whole batch ahead of
+  // their use, and handed to the issuing lane by shuffles: the issuing thread never waits on a
+  // global load.  rank < 0 marks a padding row; idx = home token (pull) or flat index (push).
+  auto load_batch = [&](long long batch, int& rank, int& idx) {
+    rank = -1;
+    idx = 0;
+    const long long j = batch * 32 + lane;
+    if (j < n) {
+      const int arr = g.row_token[first + j * n_movers];
+      if (arr >= 0) {
+        rank = rank_of(g.t, arr);
+        idx = kPull ? g.desc[arr].z : g.desc[arr].w;
+      }
+    }
+  };
+  int cur_rank, cur_idx, nxt_rank, nxt_idx;
+  load_batch(0, cur_rank, cur_idx);
+  load_batch(1, nxt_rank, nxt_idx);
+
+  // all lanes call; lane 0 issues row j (a row of the current batch `bi` or the next one)
+  auto issue = [&](long long j, long long bi) {
+    const bool in_next = (j >> 5) != bi;
+    const int rank = __shfl_sync(0xFFFFFFFFu, in_next ? nxt_rank : cur_rank, static_cast<int>(j & 31));
+    const int idx = __shfl_sync(0xFFFFFFFFu, in_next ? nxt_idx : cur_idx, static_cast<int>(j & 31));
+    if (lane != 0) return;
+    const int slot = static_cast<int>(j % g.ring);
+    uint8_t* dst = slots + static_cast<size_t>(slot) * g.slot_bytes;
+    if (rank < 0) {                      // padding row: nothing to load, complete the phase
+      mbar_arrive(bar + slot);
+      return;
+    }
+    if (kPull) {
+      mbar_arrive_expect_tx(bar + slot, static_cast<uint32_t>(g.row_bytes + g.nkb * 4));
+      bulk_load(dst, static_cast<const uint8_t*>(g.t.a[rank]) + static_cast<long long>(idx) * g.src_ld,
+                static_cast<uint32_t>(g.row_bytes), bar + slot);
+      bulk_load(dst + g.row_bytes,
+                static_cast<const float*>(g.t.b[rank]) + static_cast<long long>(idx) * g.nkb,
+                static_cast<uint32_t>(g.nkb * 4), bar + slot);
+    } else {
+      const long long p = first + j * n_movers;
+      mbar_arrive_expect_tx(bar + slot, static_cast<uint32_t>(g.row_bytes));
+      bulk_load(dst, g.y_rows + (p - g.row_begin) * g.src_ld, static_cast<uint32_t>(g.row_bytes),
+                bar + slot);
+    }
+  };
+
+  long long issued = 0, done = 0;
+  for (; issued < n && issued < depth; ++issued) issue(issued, 0);
+  bool ok = true;
+  for (long long i = 0; i < n; ++i) {
+    const long long bi = i >> 5;
+    if ((i & 31) == 0 && i > 0) {        // entering batch bi: its successor starts loading now
+      cur_rank = nxt_rank;
+      cur_idx = nxt_idx;
+      load_batch(bi + 1, nxt_rank, nxt_idx);
+    }
+    if (lane == 0) bulk_wait_read<1>();  // the store of row i-2 has left its slot
+    if (issued < n) issue(issued++, bi);
+    __syncwarp();
+    const int slot = static_cast<int>(i % g.ring);
+    const uint32_t parity = static_cast<uint32_t>(i / g.ring) & 1u;
+    // warp-uniform outcome: the shuffles below need every lane
+    if (!__all_sync(0xFFFFFFFFu,
+                    mbar_wait<20>(bar + slot, parity, abort_flag, g.status, ST_TIMEOUT_AUX))) {
+      ok = false;
+      break;
+    }
+    done = i + 1;
+    const long long p = first + i * n_movers;
+    const uint8_t* src = slots + static_cast<size_t>(slot) * g.slot_bytes;
+    const int rank = __shfl_sync(0xFFFFFFFFu, cur_rank, static_cast<int>(i & 31));
+    const int idx = __shfl_sync(0xFFFFFFFFu, cur_idx, static_cast<int>(i & 31));
+    if (kPull) {
+      uint8_t* crow = g.codes_rows + p * g.row_bytes;
+      if (rank >= 0) {
+        if (lane == 0) bulk_store(crow, src, static_cast<uint32_t>(g.row_bytes));
+      } else {
+        for (int c = lane; c < g.row_bytes / 16; c += 32)
+          reinterpret_cast<uint4*>(crow)[c] = make_uint4(0u, 0u, 0u, 0u);
+      }
+      for (int kb = lane; kb < g.nkb; kb += 32) {
+        const float sc = rank >= 0 ? reinterpret_cast<const float*>(src + g.row_bytes)[kb] : 1.0f;
+        g.scales_rows[kb * g.P_max + p] = sc;
+        if (g.atoms) {
+          const uint32_t byte = (__float_as_uint(sc) >> 23) & 0xFFu;
+          const int r = static_cast<int>(p & 127);
+          *reinterpret_cast<uint32_t*>(g.atoms + ((p >> 7) * g.nkb + kb) * 512 + (r & 31) * 16 +
+                                       (r >> 5) * 4) = byte * 0x01010101u;
+        }
+      }
+    } else if (rank >= 0 && lane == 0) {
+      bulk_store(static_cast<uint8_t*>(const_cast<void*>(g.t.a[rank])) +
+                     static_cast<long long>(idx) * g.row_bytes,
+                 src, static_cast<uint32_t>(g.row_bytes));
+    }
+    if (lane == 0) bulk_commit();        // one group per row, empty for padding rows
+    __syncwarp();
+  }
+  if (lane == 0) {
+    if (!ok) {
+      // loads already issued still target this CTA's shared memory: give each a bounded wait
+      for (long long i = done; i < issued; ++i) {
+        const int slot = static_cast<int>(i % g.ring);
+        const uint32_t parity = static_cast<uint32_t>(i / g.ring) & 1u;
+        for (int spin = 0; spin < (1 << 20) && !mbar_try_wait(bar + slot, parity); ++spin)
+          __nanosleep(1000);
+      }
+    }
+    bulk_wait_all();
+  }
+}
+
+static int mover_ring(int slot_bytes) {
+  int ring = (kMoverSmemBudget - 1024) / (kMoversPerCta * slot_bytes);
+  return ring > kMaxRing ? kMaxRing : ring;
+}
+
+template <bool kPull>
+static int launch_movers(MoverArgs& a, int payload_bytes, int ctas, cudaStream_t st) {
+  a.slot_bytes = (payload_bytes + 127) / 128 * 128;
+  a.ring = mover_ring(a.slot_bytes);
+  if (a.ring < 3) return NV41_ERR_UNSUPPORTED;
+  const size_t smem = 1024 + static_cast<size_t>(kMoversPerCta) * a.ring * a.slot_bytes;
+  static bool opted_in = false;          // per instantiation
+  if (!opted_in) {
+    if (cudaFuncSetAttribute(ep_mover_kernel<kPull>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             kMoverSmemBudget) != cudaSuccess)
+      return NV41_ERR_CUDA;
+    opted_in = true;
+  }
+  ep_mover_kernel<kPull><<<ctas, kMoversPerCta * 32, smem, st>>>(a);
+  return launch_status();
+}
+
+static bool fill_table(PeerTable& t, const void* const* a, const void* const* b,
+                       const int* arrival_offsets, int n_ranks) {
+  if (!a || !arrival_offsets || n_ranks < 1 || n_ranks > kMaxRanks) return false;
+  std::memset(&t, 0, sizeof(t));
+  t.n = n_ranks;
+  for (int g = 0; g < n_ranks; ++g) {
+    if (!a[g] || (b && !b[g])) return false;
+    t.a[g] = a[g];
+    t.b[g] = b ? b[g] : nullptr;
+    if (arrival_offsets[g + 1] < arrival_offsets[g]) return false;
+  }
+  for (int g = 0; g <= n_ranks; ++g) t.off[g] = arrival_offsets[g];
+  for (int g = n_ranks + 1; g <= kMaxRanks; ++g) t.off[g] = arrival_offsets[n_ranks];
+  return true;
+}
+
+}  // namespace nv41
+
+using namespace nv41;
+
+extern "C" int nv41_peer_alloc(unsigned long long bytes, void** dev_ptr) {
+  if (!dev_ptr || bytes == 0) return NV41_ERR_INVALID;
+  return cudaMalloc(dev_ptr, bytes) == cudaSuccess ? NV41_OK : NV41_ERR_CUDA;
+}
+
+extern "C" int nv41_peer_free(void* dev_ptr) {
+  if (!dev_ptr) return NV41_ERR_INVALID;
+  return cudaFree(dev_ptr) == cudaSuccess ? NV41_OK : NV41_ERR_CUDA;
+}
+
+extern "C" int nv41_peer_export(const void* dev_ptr, unsigned char* handle64) {
+  static_assert(sizeof(cudaIpcMemHandle_t) == NV41_PEER_HANDLE_BYTES, "IPC handle size");
+  if (!dev_ptr || !handle64) return NV41_ERR_INVALID;
+  cudaIpcMemHandle_t h;
+  if (cudaIpcGetMemHandle(&h, const_cast<void*>(dev_ptr)) != cudaSuccess) return NV41_ERR_CUDA;
+  std::memcpy(handle64, &h, sizeof(h));
+  return NV41_OK;
+}
+
+extern "C" int nv41_peer_open(const unsigned char* handle64, void** dev_ptr) {
+  if (!handle64 || !dev_ptr) return NV41_ERR_INVALID;
+  cudaIpcMemHandle_t h;
+  std::memcpy(&h, handle64, sizeof(h));
+  return cudaIpcOpenMemHandle(dev_ptr, h, cudaIpcMemLazyEnablePeerAccess) == cudaSuccess
+             ? NV41_OK
+             : NV41_ERR_CUDA;
+}
+
+extern "C" int nv41_peer_close(void* dev_ptr) {
+  if (!dev_ptr) return NV41_ERR_INVALID;
+  return cudaIpcCloseMemHandle(dev_ptr) == cudaSuccess ? NV41_OK : NV41_ERR_CUDA;
+}
+
+extern "C" int nv41_peer_copy_2d(void* dst, unsigned long long dst_pitch, const void* src,
+                                 unsigned long long src_pitch, unsigned long long width_bytes,
+                                 unsigned long long height, void* stream) {
+  if (!dst || !src || dst_pitch < width_bytes || src_pitch < width_bytes) return NV41_ERR_INVALID;
+  if (width_bytes == 0 || height == 0) return NV41_OK;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const cudaError_t err =
+      height == 1 ? cudaMemcpyAsync(dst, src, width_bytes, cudaMemcpyDefault, st)
+                  : cudaMemcpy2DAsync(dst, dst_pitch, src, src_pitch, width_bytes, height,
+                                      cudaMemcpyDefault, st);
+  return err == cudaSuccess ? NV41_OK : NV41_ERR_CUDA;
+}
+
+extern "C" int nv41_ep_pull_fp8_rows(const void* const* peer_codes,
+                                     const void* const* peer_scales, int n_ranks,
+                                     const int* arrival_offsets, const int* desc,
+                                     const int* row_token, const int* meta, int K,
+                                     long long src_ld, long long P_max, long long row_begin,
+                                     long long row_end, void* codes_rows,
+                                     float* scales_rows_kmajor, void* sf_atoms, int copy_ctas,
+                                     unsigned* status, void* stream) {
+  PeerTable t;
+  if (!fill_table(t, peer_codes, peer_scales, arrival_offsets, n_ranks) || !peer_scales ||
+      !desc || !row_token || !meta || !codes_rows || !scales_rows_kmajor || K <= 0 ||
+      (K % 128) != 0 || P_max <= 0 || (P_max % 128) != 0 || src_ld < K || (src_ld % 16) != 0 ||
+      row_begin < 0 || row_end > P_max || row_begin > row_end)
+    return NV41_ERR_INVALID;
+  if (row_begin == row_end) return NV41_OK;
+  if (copy_ctas < 0) return NV41_ERR_INVALID;
+  if (copy_ctas > 0) {
+    if ((K % 512) != 0) return NV41_ERR_UNSUPPORTED;   // bulk copies move multiples of 16 bytes
+    MoverArgs a{};
+    a.t = t;
+    a.desc = reinterpret_cast<const int4*>(desc);
+    a.row_token = row_token;
+    a.meta = meta;
+    a.row_begin = row_begin;
+    a.row_end = row_end;
+    a.row_bytes = K;
+    a.nkb = K / 128;
+    a.src_ld = src_ld;
+    a.codes_rows = static_cast<uint8_t*>(codes_rows);
+    a.scales_rows = scales_rows_kmajor;
+    a.P_max = P_max;
+    a.atoms = static_cast<uint8_t*>(sf_atoms);
+    a.status = status;
+    return launch_movers<true>(a, K + (K / 128) * 4, copy_ctas, static_cast<cudaStream_t>(stream));
+  }
+  long long blocks = (row_end - row_begin + 8 * kRowsPerWarp - 1) / (8 * kRowsPerWarp);
+  if (blocks > 148LL * 8) blocks = 148LL * 8;
+  ep_pull_fp8_rows_kernel<<<static_cast<unsigned>(blocks), 256, 0,
+                            static_cast<cudaStream_t>(stream)>>>(
+      t, reinterpret_cast<const int4*>(desc), row_token, meta, K, src_ld,
+      static_cast<uint8_t*>(codes_rows), scales_rows_kmajor, P_max,
+      static_cast<uint8_t*>(sf_atoms), row_begin, row_end);
+  return launch_status();
+}
+
+extern "C" int nv41_ep_push_rows_bf16(const void* y_rows, long long ld_y, const int* row_token,
+                                      const int* meta, const int* desc,
+                                      const int* arrival_offsets, void* const* peer_out,
+                                      int n_ranks, long long row_begin, long long row_end, int D,
+                                      int copy_ctas, unsigned* status, void* stream) {
+  PeerTable t;
+  if (!fill_table(t, const_cast<const void* const*>(peer_out), nullptr, arrival_offsets,
+                  n_ranks) ||
+      !y_rows || !row_token || !meta || !desc || row_begin < 0 || row_begin > row_end || D <= 0 ||
+      (D % 8) != 0 || ld_y < D || (ld_y % 8) != 0)
+    return NV41_ERR_INVALID;
+  if (row_begin == row_end) return NV41_OK;
+  if (copy_ctas < 0) return NV41_ERR_INVALID;
+  if (copy_ctas > 0) {
+    MoverArgs a{};
+    a.t = t;
+    a.desc = reinterpret_cast<const int4*>(desc);
+    a.row_token = row_token;
+    a.meta = meta;
+    a.row_begin = row_begin;
+    a.row_end = row_end;
+    a.row_bytes = D * 2;
+    a.src_ld = ld_y * 2;
+    a.y_rows = static_cast<const uint8_t*>(y_rows);
+    a.status = status;
+    return launch_movers<false>(a, D * 2, copy_ctas, static_cast<cudaStream_t>(stream));
+  }
+  long long blocks = (row_end - row_begin + 8 * kRowsPerWarp - 1) / (8 * kRowsPerWarp);
+  if (blocks > 148LL * 8) blocks = 148LL * 8;
+  ep_push_rows_kernel<<<static_cast<unsigned>(blocks), 256, 0,
+                        static_cast<cudaStream_t>(stream)>>>(
+      t, reinterpret_cast<const int4*>(desc), row_token, meta,
+      static_cast<const __nv_bfloat16*>(y_rows), ld_y, D, row_begin, row_end);
+  return launch_status();
+}

@@ -485,7 +485,7 @@ static int launch(const Args& a, cudaStream_t st) {
   }
   const long long units = static_cast<long long>(a.n_tiles_m) * a.n_tiles_n;
   if (units <= 0) return NV41_OK;
-  int grid = sm_count();
+  int grid = persistent_grid(sm_count());
   if (units < grid) grid = static_cast<int>(units);
   kern<<<grid, kThreads, kSmemBytes, st>>>(a);
   return launch_status();

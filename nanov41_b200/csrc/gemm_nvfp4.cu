@@ -294,7 +294,7 @@ extern "C" int nv41_moe_gemm_nvfp4(const void* a_packed, const void* a_sf, float
     configured = true;
   }
   const long long units = static_cast<long long>(g.n_tiles_m) * g.n_tiles_n;
-  int grid = sm_count();
+  int grid = persistent_grid(sm_count());
   if (units < grid) grid = static_cast<int>(units);
   fp4::nvfp4_gemm_kernel<<<grid, fp4::kThreads, fp4::kSmemBytes,
                            static_cast<cudaStream_t>(stream)>>>(g);

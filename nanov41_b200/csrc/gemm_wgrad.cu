@@ -253,7 +253,7 @@ extern "C" int nv41_moe_wgrad_bf16(const void* a_rows, const void* b_rows, const
     configured = true;
   }
   const long long units = static_cast<long long>(E) * g.tiles_m * g.tiles_n;
-  int grid = sm_count();
+  int grid = persistent_grid(sm_count());
   if (units < grid) grid = static_cast<int>(units);
   wgrad::wgrad_kernel<<<grid, wgrad::kThreads, wgrad::kSmemBytes,
                         static_cast<cudaStream_t>(stream)>>>(g);

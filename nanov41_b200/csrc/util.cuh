@@ -12,4 +12,14 @@ inline int launch_status() {
   return err == cudaSuccess ? NV41_OK : NV41_ERR_CUDA;
 }
 
+// Upper bound on the CTAs of the persistent grouped GEMMs (0 = one per SM); see
+// nv41_set_gemm_cta_limit.
+int gemm_cta_limit();
+
+// Grid of a persistent GEMM on a device with `sms` SMs.
+inline int persistent_grid(int sms) {
+  const int lim = gemm_cta_limit();
+  return (lim > 0 && lim < sms) ? lim : sms;
+}
+
 }  // namespace nv41

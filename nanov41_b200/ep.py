@@ -184,6 +184,395 @@ def _combine_slice(c, y_back, by_rank, bounds, k, shared):
     return ops.combine(y_back, pos, bounds[c + 1] - bounds[c], k, sh)
 
 
+# ------------------------------------------------------------------ peer-mapped memory path
+class _RawCuda:
+    """A device allocation seen through ``__cuda_array_interface__`` (uint8, 1-D)."""
+
+    def __init__(self, ptr: int, nbytes: int):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False),
+                                         "version": 2}
+
+
+class PeerBuffers:
+    """Named device buffers of this rank that every rank of the group maps (CUDA IPC), and this
+    rank's mappings of everybody else's.  ``own[name]`` is a uint8 view of this rank's buffer;
+    ``addr(name, g)`` the address at which rank g's buffer is mapped here (the buffer's own
+    address for this rank).  Creation and ``close`` are collective; one node, up to 8 ranks."""
+
+    def __init__(self, sizes: dict, group=None):
+        import ctypes as C
+        from . import _lib
+        self.group = group
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        if self.world > 8:
+            raise ops.Nv41Error("peer-mapped expert parallelism supports up to 8 ranks of one node")
+        self._lib = _lib.load()
+        self.dev = torch.device("cuda", torch.cuda.current_device())
+        self._own, self._opened, self._addr, self.own = {}, [], {}, {}
+        for name, nbytes in sizes.items():
+            own = C.c_void_p()
+            ops.check(self._lib.nv41_peer_alloc(nbytes, C.byref(own)), "nv41_peer_alloc")
+            self._own[name] = own.value
+            handle = (C.c_ubyte * 64)()
+            ops.check(self._lib.nv41_peer_export(own, handle), "nv41_peer_export")
+            mine = torch.tensor(list(handle), dtype=torch.uint8, device=self.dev)
+            everyone = [torch.empty_like(mine) for _ in range(self.world)]
+            dist.all_gather(everyone, mine, group=group)
+            row = []
+            for g, h in enumerate(everyone):
+                if g == self.rank:
+                    row.append(own.value)
+                    continue
+                buf = (C.c_ubyte * 64)(*h.cpu().tolist())
+                mapped = C.c_void_p()
+                ops.check(self._lib.nv41_peer_open(buf, C.byref(mapped)), "nv41_peer_open")
+                self._opened.append(mapped.value)
+                row.append(mapped.value)
+            self._addr[name] = row
+            self.own[name] = torch.as_tensor(_RawCuda(own.value, nbytes), device=self.dev)
+        self._flag = torch.zeros(1, dtype=torch.int32, device=self.dev)
+        self._streams = None
+        dist.barrier(group=group)
+
+    def addr(self, name: str, g: int) -> int:
+        return self._addr[name][g]
+
+    def addr_array(self, name: str):
+        import ctypes as C
+        return (C.c_void_p * self.world)(*self._addr[name])
+
+    def side_streams(self):
+        if self._streams is None:
+            self._streams = (torch.cuda.Stream(), torch.cuda.Stream())
+        return self._streams
+
+    def fence(self):
+        """Stream-ordered rendezvous: returns (on the stream) once every rank has reached it."""
+        dist.all_reduce(self._flag, group=self.group)
+
+    def close(self):
+        """Collective: unmap the peers' buffers, then free this rank's."""
+        torch.cuda.synchronize()
+        dist.barrier(group=self.group)
+        for p in self._opened:
+            self._lib.nv41_peer_close(p)
+        self._opened = []
+        dist.barrier(group=self.group)
+        for p in self._own.values():
+            self._lib.nv41_peer_free(p)
+        self._own = {}
+
+
+class PeerContext(PeerBuffers):
+    """Buffers of the pull / push path: ``codes`` u8 [t_max, D] and ``scales`` fp32
+    [t_max, D/128] of this rank's tokens, ``landing`` bf16 [t_max*k, D] for the expert outputs of
+    its (token, slot) rows."""
+
+    def __init__(self, t_max: int, k: int, D: int, group=None):
+        if D % 128:
+            raise ops.Nv41Error("peer-memory expert parallelism needs D % 128 == 0")
+        super().__init__({"codes": t_max * D, "scales": t_max * (D // 128) * 4,
+                          "landing": t_max * k * D * 2}, group)
+        self.t_max, self.k, self.D = t_max, k, D
+        self.codes_ptrs, self.scales_ptrs, self.landing_ptrs = (
+            self.addr_array(n) for n in ("codes", "scales", "landing"))
+        self.codes = self.own["codes"].view(t_max, D)
+        self.scales = self.own["scales"].view(torch.float32).view(t_max, D // 128)
+        self.landing = self.own["landing"].view(torch.bfloat16).view(t_max * k, D)
+        self.identity = torch.arange(t_max * k, dtype=torch.int32, device=self.dev)
+
+
+def moe_forward_fp8_peer(ctx: PeerContext, x: torch.Tensor, wq_local: ops.Fp8ExpertWeights,
+                         weights: torch.Tensor, indices: torch.Tensor, n_experts: int,
+                         limit: float, shared: torch.Tensor | None = None, slices: int = 1,
+                         copy_sms: int = 0) -> torch.Tensor:
+    """Expert-parallel forward with routed rows pulled from / pushed to peer-mapped memory.
+
+    Same arguments and result as ``moe_forward_fp8_ep``.  Per step: one all-to-all of per-peer
+    row counts (host-read), one all-to-all of 16-byte row descriptors, pull kernels, the grouped
+    GEMMs, push kernels, one one-word all-reduce as the arrival fence, the top-k sum.
+
+    With ``slices`` > 1 the owner's padded row space is cut into that many runs of whole tiles:
+    the pull of run c+1 and the push of run c-1 go on two side streams while the GEMMs of run c
+    run, and the GEMM grids are held to (SMs - ``copy_sms``) CTAs so the copy kernels find SMs.
+    """
+    import ctypes as C
+    group, world = ctx.group, ctx.world
+    T, D = x.shape
+    k = indices.shape[1]
+    e_local = n_experts // world
+    if wq_local.E != e_local:
+        raise ops.Nv41Error(f"rank holds {wq_local.E} experts, expected {e_local}")
+    if T > ctx.t_max or k != ctx.k or D != ctx.D:
+        raise ops.Nv41Error("PeerContext was sized for another problem")
+    lib = ctx._lib
+    x = x.contiguous()
+    flat = indices.reshape(-1)
+    by_rank = ops.build_layout(torch.div(flat, e_local, rounding_mode="floor"), world, k)
+    send = by_rank.counts.to(torch.int64)
+    recv = torch.empty_like(send)
+    dist.all_to_all_single(recv, send, group=group)
+    # quantise this rank's tokens into the buffer its peers read (queued before the host waits)
+    ops.check(lib.nv41_quant_fp8_1x128(x.data_ptr(), x.stride(0), None, T, D, ctx.codes.data_ptr(),
+                                       ctx.scales.data_ptr(), D // 128, 1, int(wq_local.ue8m0),
+                                       ops._stream()), "nv41_quant_fp8_1x128")
+    order = by_rank.order
+    order_l = order.long()
+    desc = torch.stack(((flat.index_select(0, order_l) % e_local).to(torch.int32),
+                        weights.reshape(-1).float().index_select(0, order_l).view(torch.int32),
+                        torch.div(order, k, rounding_mode="floor"), order), 1).contiguous()
+    both = torch.stack((send, recv)).tolist()                  # the one host synchronisation
+    sc, rc = [int(v) for v in both[0]], [int(v) for v in both[1]]
+    r_desc = exchange(desc, sc, rc, group)     # also orders every peer's quantiser before my pull
+    if sum(rc):
+        _owner_side(ctx, r_desc, rc, wq_local, e_local, limit, D, slices, copy_sms)
+    ctx.fence()                                # every rank's pushes have been issued and finished
+    return ops.combine(ctx.landing, ctx.identity, T, k, shared)
+
+
+def _owner_side(ctx, r_desc, rc, wq, e_local, limit, D, slices, copy_sms):
+    """Pull -> gate/up GEMM (+SwiGLU, re-quant) -> down GEMM -> push for the rows that arrived."""
+    import ctypes as C
+    lib, world = ctx._lib, ctx.world
+    offs = [0]
+    for c in rc:
+        offs.append(offs[-1] + c)
+    offs_c = (C.c_int * (world + 1))(*offs)
+    lay = ops.build_layout(r_desc[:, 0].contiguous(), e_local, 1,
+                           r_desc[:, 1].contiguous().view(torch.float32))
+    P, nkb = lay.P_max, D // 128
+    dev = r_desc.device
+    a_codes = torch.empty((P, D), dtype=torch.uint8, device=dev)
+    a_scale = torch.empty((nkb, P), dtype=torch.float32, device=dev)
+    a_sf = torch.zeros(P // 128 * nkb * 512, dtype=torch.uint8, device=dev) if wq.ue8m0 else None
+    st = ops.status_word(dev)
+    tiles = P // 128
+    n_sl = max(1, min(slices, tiles))
+    if D % 512:
+        n_sl = 1                  # the bulk-copy movers of the sliced path need D % 512 == 0
+    bounds = [tiles * c // n_sl * 128 for c in range(n_sl + 1)]
+    # sliced: each of the two copy streams gets half of the SMs the GEMMs leave free
+    side_ctas = max(1, copy_sms // 2) if copy_sms else 0
+
+    def pull(r0, r1, side_ctas=0):
+        ops.check(lib.nv41_ep_pull_fp8_rows(ctx.codes_ptrs, ctx.scales_ptrs, world, offs_c,
+                                            r_desc.data_ptr(), lay.row_token.data_ptr(),
+                                            lay.meta.data_ptr(), D, D, P, r0, r1,
+                                            a_codes.data_ptr(), a_scale.data_ptr(),
+                                            None if a_sf is None else a_sf.data_ptr(),
+                                            side_ctas, st.data_ptr(), ops._stream()),
+                  "nv41_ep_pull_fp8_rows")
+
+    def experts(r0, r1):
+        sub = lay.rows(r0, r1)
+        ac, asc = a_codes[r0:r1], a_scale[:, r0:r1]
+        if wq.ue8m0:
+            sf = a_sf[r0 // 128 * nkb * 512:r1 // 128 * nkb * 512]
+            h_codes, _, h_sf, _, _, _ = ops.gemm1_mx(ops.A_CONTIGUOUS, ac, None, sf, wq.w13_codes,
+                                                     wq.w13_sf, sub, limit)
+            return ops.gemm_mx(ops.A_CONTIGUOUS, h_codes, None, h_sf, wq.w2_codes, wq.w2_sf, sub)
+        h_codes, h_scale, _, _, _ = ops.gemm1_fp8(ops.A_CONTIGUOUS, ac, asc, wq.w13_codes,
+                                                  wq.w13_scale, sub, limit)
+        return ops.gemm_fp8(ops.A_CONTIGUOUS, h_codes, h_scale, wq.w2_codes, wq.w2_scale, sub)
+
+    def push(y_rows, r0, r1, side_ctas=0):
+        ops.check(lib.nv41_ep_push_rows_bf16(y_rows.data_ptr(), y_rows.stride(0),
+                                             lay.row_token.data_ptr(), lay.meta.data_ptr(),
+                                             r_desc.data_ptr(), offs_c, ctx.landing_ptrs, world,
+                                             r0, r1, D, side_ctas, st.data_ptr(), ops._stream()),
+                  "nv41_ep_push_rows_bf16")
+
+    if n_sl == 1:
+        pull(0, P)
+        push(experts(0, P), 0, P)
+        return
+    # first pull and last push have nothing to hide behind: wide grids on the main stream
+    main = torch.cuda.current_stream()
+    pull_s, push_s = ctx.side_streams()
+    ready = torch.cuda.Event()
+    ready.record(main)
+    pull_s.wait_event(ready)
+    pulled = [None]
+    with torch.cuda.stream(pull_s):
+        for c in range(1, n_sl):
+            pull(bounds[c], bounds[c + 1], side_ctas)
+            ev = torch.cuda.Event()
+            ev.record(pull_s)
+            pulled.append(ev)
+    pull(bounds[0], bounds[1])
+    if copy_sms:
+        ops.set_gemm_cta_limit(max(1, torch.cuda.get_device_properties(dev).multi_processor_count
+                                   - copy_sms))
+    keep = []
+    try:
+        for c in range(n_sl):
+            if pulled[c] is not None:
+                main.wait_event(pulled[c])
+            y_rows = experts(bounds[c], bounds[c + 1])
+            keep.append(y_rows)
+            if c == n_sl - 1:
+                push(y_rows, bounds[c], bounds[c + 1])
+                break
+            done = torch.cuda.Event()
+            done.record(main)
+            with torch.cuda.stream(push_s):
+                push_s.wait_event(done)
+                push(y_rows, bounds[c], bounds[c + 1], side_ctas)
+    finally:
+        if copy_sms:
+            ops.set_gemm_cta_limit(0)
+    joined = torch.cuda.Event()
+    joined.record(push_s)
+    main.wait_event(joined)      # side-stream work ends before anything later on this stream
+
+
+# ------------------------------------------------------- segment path (copy engines only)
+class SegContext(PeerBuffers):
+    """Buffers of the segment path.  Every rank lays ITS routed rows out expert-major over ALL
+    experts (each expert's run padded to 128 rows) in peer-mapped buffers: FP8 codes [P, D], K-major
+    scales [D/128, P], router weight per row [P], local expert id per 128-row tile [P/128] (and
+    the e8m0 scale atoms for ue8m0 weights), plus ``y`` bf16 [P, D] for the results.  The rows of
+    the experts a rank owns are then one contiguous run of tiles in every rank's buffers."""
+
+    def __init__(self, t_max: int, k: int, n_experts: int, D: int, ue8m0: bool = False, group=None):
+        if D % 128:
+            raise ops.Nv41Error("expert parallelism needs D % 128 == 0")
+        P = ops.p_max_for(t_max * k, n_experts)
+        nkb = D // 128
+        sizes = {"codes": P * D, "scales": nkb * P * 4, "weight": P * 4, "tiles": P // 128 * 4,
+                 "y": P * D * 2}
+        if ue8m0:
+            sizes["atoms"] = P // 128 * nkb * 512
+        super().__init__(sizes, group)
+        self.t_max, self.k, self.E, self.D, self.P, self.ue8m0 = t_max, k, n_experts, D, P, ue8m0
+        self.dummy = torch.zeros(1, dtype=torch.int32, device=self.dev)
+
+    def copy(self, dst: int, dst_pitch: int, src: int, src_pitch: int, width: int, height: int = 1):
+        """Copy-engine copy on the current stream (addresses and pitches in bytes)."""
+        ops.check(self._lib.nv41_peer_copy_2d(dst, dst_pitch, src, src_pitch, width, height,
+                                              ops._stream()), "nv41_peer_copy_2d")
+
+
+def moe_forward_fp8_seg(ctx: SegContext, x: torch.Tensor, wq_local: ops.Fp8ExpertWeights,
+                        weights: torch.Tensor, indices: torch.Tensor, n_experts: int,
+                        limit: float, shared: torch.Tensor | None = None,
+                        slice_rows: int = 65536) -> torch.Tensor:
+    """Expert-parallel forward in which no kernel moves rows between ranks.
+
+    Same arguments and result as ``moe_forward_fp8_ep``.  The home rank quantises its tokens once
+    and permutes them into its padded expert-major layout over all experts (the single-GPU
+    layout); the owner of experts [o*E/G, (o+1)*E/G) copies that contiguous run of every peer's
+    buffers into scratch with the copy engines (slices of ``slice_rows`` rows, on a side stream,
+    while the GEMMs of earlier slices run on all SMs), runs the grouped GEMMs on it, and copies
+    the bf16 results back into the home rank's ``y`` at the same rows on a second side stream.
+    Its own run is used in place, split around the peers' slices.  One all-gather of G+2 integers per rank (host-read) gives
+    the run boundaries and orders "peer's buffers are ready" before the copies; a one-word
+    all-reduce fences the results before the top-k sum."""
+    from dataclasses import replace
+    world, me, dev = ctx.world, ctx.rank, ctx.dev
+    T, D = x.shape
+    k = indices.shape[1]
+    El = n_experts // world
+    nkb = D // 128
+    if wq_local.E != El:
+        raise ops.Nv41Error(f"rank holds {wq_local.E} experts, expected {El}")
+    if T > ctx.t_max or k != ctx.k or D != ctx.D or n_experts != ctx.E or wq_local.ue8m0 != ctx.ue8m0:
+        raise ops.Nv41Error("SegContext was sized for another problem")
+    lay = ops.build_layout(indices.reshape(-1), n_experts, k, weights.reshape(-1))
+    P = lay.P_max
+    own = ctx.own
+    codes = own["codes"][:P * D].view(P, D)
+    scales = own["scales"].view(torch.float32)[:nkb * P].view(nkb, P)
+    atoms = None
+    if ctx.ue8m0:
+        atoms = own["atoms"][:P // 128 * nkb * 512]
+        atoms.zero_()
+    y_mine = own["y"].view(torch.bfloat16)[:P * D].view(P, D)
+    x_codes, x_scale = ops.quant_fp8_1x128(x.contiguous(), scale_kmajor=True, ue8m0=ctx.ue8m0)
+    ops.gather_fp8_rows(x_codes, x_scale, lay, ctx.ue8m0, out=(codes, scales, atoms))
+    w_rows = own["weight"].view(torch.float32)[:P]
+    w_rows.copy_(lay.row_weight)
+    t_rows = own["tiles"].view(torch.int32)[:P // 128]
+    te = lay.tile_expert
+    t_rows.copy_(torch.where(te >= 0, te % El, te))
+    mine = torch.cat((lay.pad_off[::El], torch.tensor([P], dtype=torch.int32, device=dev)))
+    everyone = torch.empty((world, world + 2), dtype=torch.int32, device=dev)
+    dist.all_gather_into_tensor(everyone, mine.contiguous(), group=ctx.group)
+    B = everyone.tolist()                       # the one host synchronisation
+
+    def experts(ac, asc, sf, w, tiles, out):
+        n = ac.shape[0]
+        sub = replace(lay, P_max=n, tile_expert=tiles, row_weight=w, row_token=ctx.dummy,
+                      flat_of_row=ctx.dummy)
+        if ctx.ue8m0:
+            h_codes, _, h_sf, _, _, _ = ops.gemm1_mx(ops.A_CONTIGUOUS, ac, None, sf,
+                                                     wq_local.w13_codes, wq_local.w13_sf, sub, limit)
+            return ops.gemm_mx(ops.A_CONTIGUOUS, h_codes, None, h_sf, wq_local.w2_codes,
+                               wq_local.w2_sf, sub, out=out)
+        h_codes, h_scale, _, _, _ = ops.gemm1_fp8(ops.A_CONTIGUOUS, ac, asc, wq_local.w13_codes,
+                                                  wq_local.w13_scale, sub, limit)
+        return ops.gemm_fp8(ops.A_CONTIGUOUS, h_codes, h_scale, wq_local.w2_codes,
+                            wq_local.w2_scale, sub, out=out)
+
+    main = torch.cuda.current_stream()
+    cin, cout = ctx.side_streams()
+    ready = torch.cuda.Event()
+    ready.record(main)
+    cin.wait_event(ready)
+    slice_rows = max(128, slice_rows // 128 * 128)
+    jobs = []
+    with torch.cuda.stream(cin):
+        for i in range(1, world):
+            g = (me + i) % world
+            r0, r1, Pg = B[g][me], B[g][me + 1], B[g][world + 1]
+            for s0 in range(r0, r1, slice_rows):
+                n = min(slice_rows, r1 - s0)
+                ac = torch.empty((n, D), dtype=torch.uint8, device=dev)
+                asc = torch.empty((nkb, n), dtype=torch.float32, device=dev)
+                w = torch.empty(n, dtype=torch.float32, device=dev)
+                tiles = torch.empty(n // 128, dtype=torch.int32, device=dev)
+                sf = torch.empty(n // 128 * nkb * 512, dtype=torch.uint8, device=dev) if ctx.ue8m0 else None
+                ctx.copy(ac.data_ptr(), n * D, ctx.addr("codes", g) + s0 * D, n * D, n * D)
+                ctx.copy(asc.data_ptr(), n * 4, ctx.addr("scales", g) + s0 * 4, Pg * 4, n * 4, nkb)
+                ctx.copy(w.data_ptr(), n * 4, ctx.addr("weight", g) + s0 * 4, n * 4, n * 4)
+                ctx.copy(tiles.data_ptr(), n // 32, ctx.addr("tiles", g) + s0 // 32, n // 32, n // 32)
+                if sf is not None:
+                    nb = n // 128 * nkb * 512
+                    ctx.copy(sf.data_ptr(), nb, ctx.addr("atoms", g) + s0 // 128 * nkb * 512, nb, nb)
+                ev = torch.cuda.Event()
+                ev.record(cin)
+                jobs.append((g, s0, n, ac, asc, sf, w, tiles, ev))
+    # this rank's own run is used in place, half before and half after the peers' slices: the
+    # first half hides the first copy-in, the second the last copy-out
+    r0, r1 = B[me][me], B[me][me + 1]
+    mid = r0 + (r1 - r0) // 256 * 128
+
+    def own_run(a, b):
+        if b > a:
+            experts(codes[a:b], scales[:, a:b],
+                    None if atoms is None else atoms[a // 128 * nkb * 512:b // 128 * nkb * 512],
+                    w_rows[a:b], t_rows[a // 128:b // 128], y_mine[a:b])
+
+    own_run(r0, mid)
+    keep = []
+    for g, s0, n, ac, asc, sf, w, tiles, ev in jobs:
+        main.wait_event(ev)
+        y = experts(ac, asc, sf, w, tiles, None)
+        keep.append(y)
+        done = torch.cuda.Event()
+        done.record(main)
+        with torch.cuda.stream(cout):
+            cout.wait_event(done)
+            ctx.copy(ctx.addr("y", g) + s0 * D * 2, n * D * 2, y.data_ptr(), n * D * 2, n * D * 2)
+    own_run(mid, r1)
+    for side in (cin, cout):                     # side-stream work ends before anything later here
+        joined = torch.cuda.Event()
+        joined.record(side)
+        main.wait_event(joined)
+    ctx.fence()                                  # every rank's results have landed
+    return ops.combine(y_mine, lay.row_of_flat, T, k, shared)
+
+
 def shard_expert_weights(w1, w3, w2, rank: int, world: int):
     """Rows [rank*E/world, (rank+1)*E/world) of stacked [E, ...] weights."""
     e_local = w1.shape[0] // world

@@ -144,6 +144,23 @@ class DeviceLayout:
     meta: torch.Tensor
     status: torch.Tensor
 
+    def rows(self, r0: int, r1: int) -> "DeviceLayout":
+        """The slice [r0, r1) of the padded row space (multiples of 128) as a layout of its own
+        for the grouped GEMMs: per-row and per-tile tables are views, the per-expert tables and
+        ``meta`` still describe the whole space."""
+        if r0 % BM or r1 % BM or not 0 <= r0 <= r1 <= self.P_max:
+            raise Nv41Error("row slices of a layout are cut at multiples of 128")
+        from dataclasses import replace
+        return replace(self, P_max=r1 - r0, row_token=self.row_token[r0:r1],
+                       flat_of_row=self.flat_of_row[r0:r1],
+                       row_weight=None if self.row_weight is None else self.row_weight[r0:r1],
+                       tile_expert=self.tile_expert[r0 // BM:r1 // BM])
+
+
+def set_gemm_cta_limit(max_ctas: int) -> None:
+    """Upper bound on the CTAs of the persistent grouped GEMMs (0 = one per SM)."""
+    check(_lib.load().nv41_set_gemm_cta_limit(int(max_ctas)), "nv41_set_gemm_cta_limit")
+
 
 def p_max_for(R: int, E: int) -> int:
     """Rows allocated for the padded space (nanov41/triton_grouped_moe.py:473-474, BM = 128)."""
@@ -241,13 +258,14 @@ def gemm1_fp8(a_mode: int, a_codes: torch.Tensor, a_scale_kmajor: torch.Tensor,
 
 def gemm_fp8(a_mode: int, a_codes: torch.Tensor, a_scale_kmajor: torch.Tensor,
              b_codes: torch.Tensor, b_scale: torch.Tensor, layout: DeviceLayout,
-             b_scale_transposed: bool = False) -> torch.Tensor:
+             b_scale_transposed: bool = False, out: torch.Tensor | None = None) -> torch.Tensor:
     """Grouped C = A @ B_e^T (bf16 [P_max, N]); b_codes uint8 [E, N, K]; b_scale fp32
     [E, ceil(N/128), K/128], or [E, K/128, ceil(N/128)] with ``b_scale_transposed``."""
     _need_cuda(a_codes, a_scale_kmajor, b_codes, b_scale)
     E, N, K = b_codes.shape
     P = layout.P_max
-    out = torch.empty((P, N), dtype=torch.bfloat16, device=a_codes.device)
+    if out is None:
+        out = torch.empty((P, N), dtype=torch.bfloat16, device=a_codes.device)
     bs_e = b_scale.stride(0)
     if b_scale_transposed:
         bs_nb, bs_kb = b_scale.stride(2), b_scale.stride(1)
@@ -288,12 +306,13 @@ def gemm1_mx(a_mode: int, a_codes, a_scale_kmajor, a_sf, w13_codes, w13_sf, layo
 
 
 def gemm_mx(a_mode: int, a_codes, a_scale_kmajor, a_sf, b_codes, b_sf,
-            layout: DeviceLayout) -> torch.Tensor:
+            layout: DeviceLayout, out: torch.Tensor | None = None) -> torch.Tensor:
     """ue8m0 counterpart of ``gemm_fp8``: grouped C = A @ B_e^T, bf16 [P_max, N]."""
     _need_cuda(a_codes, b_codes, b_sf)
     E, N, K = b_codes.shape
     P = layout.P_max
-    out = torch.empty((P, N), dtype=torch.bfloat16, device=a_codes.device)
+    if out is None:
+        out = torch.empty((P, N), dtype=torch.bfloat16, device=a_codes.device)
     st = status_word(a_codes.device)
     check(_lib.load().nv41_moe_gemm_mx(
         a_mode, _ptr(a_codes), a_codes.stride(0), _ptr(a_scale_kmajor),
@@ -376,16 +395,20 @@ def gather_rows(src: torch.Tensor, rows: torch.Tensor) -> torch.Tensor:
 
 
 def gather_fp8_rows(codes: torch.Tensor, scales_kmajor: torch.Tensor, layout: DeviceLayout,
-                    with_atoms: bool = False):
+                    with_atoms: bool = False, out=None):
     """Per-token FP8 rows -> padded expert-major order: (codes [P_max, K], scales [K/128, P_max],
     e8m0 scale atoms | None)."""
     _need_cuda(codes, scales_kmajor)
     T, K = codes.shape
     P = layout.P_max
     dev = codes.device
-    out = torch.empty((P, K), dtype=torch.uint8, device=dev)
-    sc = torch.empty((K // 128, P), dtype=torch.float32, device=dev)
-    atoms = torch.zeros(P // 128 * (K // 128) * 512, dtype=torch.uint8, device=dev) if with_atoms else None
+    if out is not None:
+        out, sc, atoms = out          # caller's buffers of exactly these shapes (atoms zeroed)
+    else:
+        out = torch.empty((P, K), dtype=torch.uint8, device=dev)
+        sc = torch.empty((K // 128, P), dtype=torch.float32, device=dev)
+        atoms = (torch.zeros(P // 128 * (K // 128) * 512, dtype=torch.uint8, device=dev)
+                 if with_atoms else None)
     check(_lib.load().nv41_gather_fp8_rows(_ptr(codes), codes.stride(0), _ptr(scales_kmajor),
                                            scales_kmajor.stride(0), _ptr(layout.row_token),
                                            _ptr(layout.meta), K, P, _ptr(out), _ptr(sc),

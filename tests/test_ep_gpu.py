@@ -45,6 +45,37 @@ def _worker(rank, world, port):
         single = ops.moe_forward_fp8(g["x"][sl], wq_all, g["weights"][sl], g["indices"][sl], 10.0,
                                      shared)
         assert torch.equal(out, single)
+        # rows pulled from / pushed to peer-mapped memory by the owner's kernels: two steps in a
+        # row through the same buffers, the second with other tokens
+        ctx = ep.PeerContext(T, CASE["k"], CASE["D"])
+        peer1 = ep.moe_forward_fp8_peer(ctx, g["x"][sl], wq_local, g["weights"][sl],
+                                        g["indices"][sl], CASE["E"], 10.0, shared)
+        x2 = g["x"][sl].flip(0).contiguous()
+        peer2 = ep.moe_forward_fp8_peer(ctx, x2, wq_local, g["weights"][sl], g["indices"][sl],
+                                        CASE["E"], 10.0, shared)
+        peer3 = ep.moe_forward_fp8_peer(ctx, x2, wq_local, g["weights"][sl], g["indices"][sl],
+                                        CASE["E"], 10.0, shared, slices=3, copy_sms=8)
+        single2 = ops.moe_forward_fp8(x2, wq_all, g["weights"][sl], g["indices"][sl], 10.0, shared)
+        ops.check_status()
+        assert torch.equal(peer1, single)
+        assert torch.equal(peer2, single2)
+        assert torch.equal(peer3, single2)
+        ctx.close()
+        # rows stay in the home rank's expert-major layout; the owner copies its run of tiles
+        # with the copy engines (slices of 128 rows here, so several slices per peer)
+        for ue8m0 in (False, True):
+            seg = ep.SegContext(T, CASE["k"], CASE["E"], CASE["D"], ue8m0=ue8m0)
+            wl = wq_local if not ue8m0 else ops.quantize_expert_weights(
+                w1.contiguous(), w3.contiguous(), w2.contiguous(), ue8m0=True)
+            wa = wq_all if not ue8m0 else ops.quantize_expert_weights(g["w1"], g["w3"], g["w2"],
+                                                                      ue8m0=True)
+            for xs in (g["x"][sl], x2):
+                got = ep.moe_forward_fp8_seg(seg, xs, wl, g["weights"][sl], g["indices"][sl],
+                                             CASE["E"], 10.0, shared, slice_rows=128)
+                want = ops.moe_forward_fp8(xs, wa, g["weights"][sl], g["indices"][sl], 10.0, shared)
+                ops.check_status()
+                assert torch.equal(got, want), ue8m0
+            seg.close()
         ref = OM.moe_fp8(c["x"][sl], c["w1"], c["w3"], c["w2"], c["weights"][sl], c["indices"][sl],
                          10.0, shared=shared.cpu())
         mx, mean = OM.rel_errors(out.cpu(), ref)
