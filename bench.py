@@ -139,8 +139,8 @@ def c5_config(world):
     return {"workload": "config5: expert-parallel FP8 MoE forward, E=256 top-8 uniform-random "
                         "logits seed 2, D=2048 I=1024, 131072 tokens per step over the box",
             "E": 256, "T": 131072, "k": 8, "D": 2048, "I": 1024,
-            "parallelism": f"ep{world} (experts sharded, tokens data-parallel, NCCL all-to-all "
-                           "dispatch of fp8 rows / combine of bf16 rows)",
+            "parallelism": f"ep{world} (experts sharded, tokens data-parallel; fp8 rows out and bf16 "
+                           "rows back over NVLink, see ep_mode)",
             "l2": "inputs_exceed_l2", "weights": "block-quantised once outside the timed region"}
 
 
@@ -551,7 +551,7 @@ def main():
     ap.add_argument("--cpu-sample-tokens", type=int, default=16384)
     ap.add_argument("--ep-chunks", type=int, default=1,
                     help="N > 1: token slices whose all-to-alls overlap the previous slice's GEMMs")
-    ap.add_argument("--ep-mode", default="nccl", choices=["nccl", "peer", "segments"],
+    ap.add_argument("--ep-mode", default="segments", choices=["nccl", "peer", "segments"],
                     help="N > 1: rows travel through NCCL all-to-alls, or are pulled from / pushed to "
                          "peer-mapped memory by the owner's own kernels")
     ap.add_argument("--ep-slice-rows", type=int, default=65536,
