@@ -271,6 +271,47 @@ int nv41_peer_copy_2d(void* dst, unsigned long long dst_pitch, const void* src,
                       unsigned long long src_pitch, unsigned long long width_bytes,
                       unsigned long long height, void* stream);
 
+/* Owner side of the segment path in one host call.  Every rank keeps its routed rows expert-major
+ * over ALL experts (the single-GPU layout of nv41_moe_layout_build, rows gathered with
+ * nv41_gather_fp8_rows) in peer-mapped buffers: codes u8 [P, D], scales fp32 [D/128][P], router
+ * weight fp32 [P], local expert id per 128-row tile int32 [P/128] (-1 = unused), e8m0 scale atoms
+ * (ue8m0 only), and y bf16 [P, D] for the results.  bounds (HOST, [n_ranks][n_ranks + 2]) holds per
+ * rank g the first padded row of every owner's experts, the end of the last owner's, and P of
+ * rank g.  This rank (`me`) copies its run of every peer's buffers into scratch with the copy
+ * engines on copy_in_stream (slices of slice_rows rows), runs nv41_moe_gemm1_* / nv41_moe_gemm_*
+ * on main_stream for each slice and for its own run (in place, split around the peers' slices),
+ * and copies each slice's results into the peer's y on copy_out_stream; main_stream is made to
+ * wait for both side streams before the call returns (nothing is synchronised on the host).
+ * The caller orders "peers' buffers ready" before and "results landed" after with collectives. */
+typedef struct nv41_ep_weights {
+  const void* w13_codes;  /* u8 [E_local, 2I, D] */
+  const void* w13_scale;  /* fp32 [E_local, 2I/128, D/128], or e8m0 atoms when ue8m0 */
+  const void* w2_codes;   /* u8 [E_local, D, I] */
+  const void* w2_scale;   /* fp32 block scales with the strides below, or e8m0 atoms */
+  long long w2_bs_e, w2_bs_nb, w2_bs_kb;
+  int E_local, I, D, ue8m0;
+  float limit;
+} nv41_ep_weights;
+typedef struct nv41_ep_scratch {
+  void* a_codes;    /* u8 [remote_rows_cap, D] */
+  float* a_scale;   /* fp32 [D/128][remote_rows_cap] */
+  float* a_weight;  /* fp32 [remote_rows_cap] */
+  int* a_tiles;     /* int32 [remote_rows_cap/128] */
+  void* a_atoms;    /* ue8m0: u8 [remote_rows_cap/128][D/128][512] */
+  void* y;          /* bf16 [remote_rows_cap, D] */
+  long long remote_rows_cap;
+  void* h_codes;    /* u8 [h_rows_cap, I] */
+  float* h_scale;   /* fp32 [I/128 * h_rows_cap] */
+  void* h_sf;       /* ue8m0: u8 [h_rows_cap/128][I/128][512] */
+  long long h_rows_cap; /* >= rows of the largest slice and of each half of the own run */
+} nv41_ep_scratch;
+int nv41_ep_owner_forward(const long long* bounds, int n_ranks, int me, long long slice_rows,
+                          const void* const* peer_codes, const void* const* peer_scales,
+                          const void* const* peer_weight, const void* const* peer_tiles,
+                          const void* const* peer_atoms, void* const* peer_y,
+                          const nv41_ep_weights* w, const nv41_ep_scratch* s, unsigned* status,
+                          void* main_stream, void* copy_in_stream, void* copy_out_stream);
+
 /* Pull the FP8 rows routed to this rank out of the home ranks' buffers into the padded
  * expert-major operand (the permute of nanov41/fast_moe.py:399 done across ranks):
  * row p with arrival index a = row_token[p] >= 0, a in [arrival_offsets[g], arrival_offsets[g+1]),

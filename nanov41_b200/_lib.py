@@ -16,6 +16,22 @@ _ERR_NAMES = {ERR_INVALID: "invalid argument", ERR_CUDA: "CUDA launch/driver err
 
 _p, _i, _ll, _f = C.c_void_p, C.c_int, C.c_longlong, C.c_float
 
+class EpWeights(C.Structure):
+    """nv41_ep_weights"""
+    _fields_ = [("w13_codes", C.c_void_p), ("w13_scale", C.c_void_p), ("w2_codes", C.c_void_p),
+                ("w2_scale", C.c_void_p), ("w2_bs_e", C.c_longlong), ("w2_bs_nb", C.c_longlong),
+                ("w2_bs_kb", C.c_longlong), ("E_local", C.c_int), ("I", C.c_int), ("D", C.c_int),
+                ("ue8m0", C.c_int), ("limit", C.c_float)]
+
+
+class EpScratch(C.Structure):
+    """nv41_ep_scratch"""
+    _fields_ = [("a_codes", C.c_void_p), ("a_scale", C.c_void_p), ("a_weight", C.c_void_p),
+                ("a_tiles", C.c_void_p), ("a_atoms", C.c_void_p), ("y", C.c_void_p),
+                ("remote_rows_cap", C.c_longlong), ("h_codes", C.c_void_p), ("h_scale", C.c_void_p),
+                ("h_sf", C.c_void_p), ("h_rows_cap", C.c_longlong)]
+
+
 # name -> (restype, argtypes); mirrors include/nanov41_b200.h declaration by declaration
 SIGNATURES = {
     "nv41_abi_version": (_i, []),
@@ -58,6 +74,7 @@ SIGNATURES = {
                                    _i, _p, _p]),
     "nv41_ep_push_rows_bf16": (_i, [_p, _ll, _p, _p, _p, _p, _p, _i, _ll, _ll, _i, _i, _p, _p]),
     "nv41_set_gemm_cta_limit": (_i, [_i]),
+    "nv41_ep_owner_forward": (_i, [_p, _i, _i, _ll, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p]),
 }
 
 _lib = None

@@ -1,0 +1,172 @@
+// Owner side of the expert-parallel segment path as one host call: copy-engine transfers of the
+// peers' runs of tiles into scratch, the grouped FP8 GEMMs on every run, copy-engine transfers of
+// the results back, with the stream / event choreography kept out of the interpreter (at 8 ranks
+// a step is some sixty enqueue operations).
+//
+// Every rank holds ITS routed rows expert-major over all experts in peer-mapped buffers (see
+// nanov41_b200/ep.py, SegContext).  bounds[g] = {first row of owner 0's experts, ..., of owner
+// G-1's, end of the last owner's, P of rank g}: the rows this rank owns in rank g's buffers are
+// [bounds[g][me], bounds[g][me+1]).
+#include <cuda_runtime.h>
+#include <cstdint>
+#include <vector>
+
+#include "../../include/nanov41_b200.h"
+#include "util.cuh"
+
+namespace {
+
+struct Slice {
+  int g;
+  long long s0, n, off, Pg;
+};
+
+cudaEvent_t pooled_event(size_t i) {
+  thread_local std::vector<cudaEvent_t> pool;
+  while (pool.size() <= i) {
+    cudaEvent_t e = nullptr;
+    if (cudaEventCreateWithFlags(&e, cudaEventDisableTiming) != cudaSuccess) return nullptr;
+    pool.push_back(e);
+  }
+  return pool[i];
+}
+
+inline const uint8_t* at(const void* base, long long bytes) {
+  return static_cast<const uint8_t*>(base) + bytes;
+}
+inline uint8_t* at(void* base, long long bytes) { return static_cast<uint8_t*>(base) + bytes; }
+
+}  // namespace
+
+extern "C" int nv41_ep_owner_forward(const long long* bounds, int n_ranks, int me,
+                                     long long slice_rows, const void* const* peer_codes,
+                                     const void* const* peer_scales,
+                                     const void* const* peer_weight,
+                                     const void* const* peer_tiles,
+                                     const void* const* peer_atoms, void* const* peer_y,
+                                     const nv41_ep_weights* w, const nv41_ep_scratch* s,
+                                     unsigned* status, void* main_stream, void* copy_in_stream,
+                                     void* copy_out_stream) {
+  if (!bounds || !peer_codes || !peer_scales || !peer_weight || !peer_tiles || !peer_y || !w ||
+      !s || n_ranks < 1 || n_ranks > NV41_EP_MAX_RANKS || me < 0 || me >= n_ranks ||
+      slice_rows < 128 || (slice_rows % 128) != 0 || w->D <= 0 || (w->D % 128) != 0 ||
+      w->I <= 0 || (w->I % 128) != 0 || (w->ue8m0 && !peer_atoms))
+    return NV41_ERR_INVALID;
+  const int G = n_ranks, D = w->D, I = w->I, nkb = D / 128;
+  cudaStream_t main = static_cast<cudaStream_t>(main_stream);
+  cudaStream_t cin = static_cast<cudaStream_t>(copy_in_stream);
+  cudaStream_t cout = static_cast<cudaStream_t>(copy_out_stream);
+  auto B = [&](int g, int j) { return bounds[static_cast<long long>(g) * (G + 2) + j]; };
+
+  std::vector<Slice> slices;
+  long long off = 0, h_need = 0;
+  for (int i = 1; i < G; ++i) {
+    const int g = (me + i) % G;
+    const long long r0 = B(g, me), r1 = B(g, me + 1), Pg = B(g, G + 1);
+    if (r0 < 0 || r1 < r0 || r1 > Pg || (r0 % 128) != 0 || (r1 % 128) != 0)
+      return NV41_ERR_INVALID;
+    for (long long s0 = r0; s0 < r1; s0 += slice_rows) {
+      const long long n = (r1 - s0) < slice_rows ? (r1 - s0) : slice_rows;
+      slices.push_back({g, s0, n, off, Pg});
+      off += n;
+      if (n > h_need) h_need = n;
+    }
+  }
+  const long long o0 = B(me, me), o1 = B(me, me + 1), Pme = B(me, G + 1);
+  if (o0 < 0 || o1 < o0 || o1 > Pme || (o0 % 128) != 0 || (o1 % 128) != 0) return NV41_ERR_INVALID;
+  const long long omid = o0 + (o1 - o0) / 256 * 128;
+  if (omid - o0 > h_need) h_need = omid - o0;
+  if (o1 - omid > h_need) h_need = o1 - omid;
+  if (off > s->remote_rows_cap || h_need > s->h_rows_cap) return NV41_ERR_INVALID;
+  const long long cap = s->remote_rows_cap;
+
+  auto ok = [](cudaError_t e) { return e == cudaSuccess; };
+  size_t n_ev = 0;
+  auto order = [&](cudaStream_t from, cudaStream_t to) {   // `to` waits for what `from` holds now
+    cudaEvent_t e = pooled_event(n_ev++);
+    return e && ok(cudaEventRecord(e, from)) && ok(cudaStreamWaitEvent(to, e, 0));
+  };
+
+  // gate/up GEMM (+SwiGLU, re-quantisation) and down GEMM on `rows` padded rows
+  auto experts = [&](const void* a_codes, const float* a_scale, long long a_scale_stride,
+                     const void* a_atoms, const float* weight, const int* tiles, long long rows,
+                     void* y_out) -> int {
+    if (rows == 0) return NV41_OK;
+    int rc;
+    if (w->ue8m0) {
+      const size_t sf_bytes = static_cast<size_t>(rows / 128) * (I / 128) * 512;
+      if (!ok(cudaMemsetAsync(s->h_sf, 0, sf_bytes, main))) return NV41_ERR_CUDA;
+      rc = nv41_moe_gemm1_mx(NV41_A_CONTIGUOUS, a_codes, D, nullptr, 0, a_atoms, rows,
+                             w->w13_codes, w->w13_scale, w->E_local, I, D, tiles, tiles, weight,
+                             rows, w->limit, s->h_codes, s->h_scale, s->h_sf, nullptr, nullptr,
+                             nullptr, status, main);
+      if (rc != NV41_OK) return rc;
+      return nv41_moe_gemm_mx(NV41_A_CONTIGUOUS, s->h_codes, I, nullptr, 0, s->h_sf, rows,
+                              w->w2_codes, w->w2_scale, w->E_local, D, I, tiles, tiles, rows,
+                              y_out, D, status, main);
+    }
+    rc = nv41_moe_gemm1_fp8(NV41_A_CONTIGUOUS, a_codes, D, D, a_scale, a_scale_stride, rows,
+                            w->w13_codes, static_cast<const float*>(w->w13_scale), w->E_local, I,
+                            D, tiles, tiles, weight, rows, w->limit, s->h_codes, s->h_scale,
+                            nullptr, nullptr, nullptr, status, main);
+    if (rc != NV41_OK) return rc;
+    return nv41_moe_gemm_fp8(NV41_A_CONTIGUOUS, s->h_codes, I, s->h_scale, rows, rows,
+                             w->w2_codes, static_cast<const float*>(w->w2_scale), w->w2_bs_e,
+                             w->w2_bs_nb, w->w2_bs_kb, w->E_local, D, I, tiles, tiles, rows,
+                             y_out, D, status, main);
+  };
+  auto own_run = [&](long long a, long long b) -> int {
+    return experts(at(peer_codes[me], a * D),
+                   reinterpret_cast<const float*>(at(peer_scales[me], a * 4)), Pme,
+                   w->ue8m0 ? at(peer_atoms[me], a / 128 * nkb * 512) : nullptr,
+                   reinterpret_cast<const float*>(at(peer_weight[me], a * 4)),
+                   reinterpret_cast<const int*>(at(peer_tiles[me], a / 128 * 4)), b - a,
+                   at(peer_y[me], a * D * 2));
+  };
+
+  // copy-ins: everything queued now on the copy-in stream, one event per slice
+  if (!order(main, cin)) return NV41_ERR_CUDA;
+  std::vector<cudaEvent_t> arrived(slices.size());
+  for (size_t j = 0; j < slices.size(); ++j) {
+    const Slice& sl = slices[j];
+    const bool copied =
+        ok(cudaMemcpyAsync(at(s->a_codes, sl.off * D), at(peer_codes[sl.g], sl.s0 * D),
+                           static_cast<size_t>(sl.n) * D, cudaMemcpyDefault, cin)) &&
+        ok(cudaMemcpy2DAsync(s->a_scale + sl.off, static_cast<size_t>(cap) * 4,
+                             at(peer_scales[sl.g], sl.s0 * 4), static_cast<size_t>(sl.Pg) * 4,
+                             static_cast<size_t>(sl.n) * 4, nkb, cudaMemcpyDefault, cin)) &&
+        ok(cudaMemcpyAsync(s->a_weight + sl.off, at(peer_weight[sl.g], sl.s0 * 4),
+                           static_cast<size_t>(sl.n) * 4, cudaMemcpyDefault, cin)) &&
+        ok(cudaMemcpyAsync(s->a_tiles + sl.off / 128, at(peer_tiles[sl.g], sl.s0 / 128 * 4),
+                           static_cast<size_t>(sl.n / 128) * 4, cudaMemcpyDefault, cin)) &&
+        (!w->ue8m0 ||
+         ok(cudaMemcpyAsync(at(s->a_atoms, sl.off / 128 * nkb * 512),
+                            at(peer_atoms[sl.g], sl.s0 / 128 * nkb * 512),
+                            static_cast<size_t>(sl.n / 128) * nkb * 512, cudaMemcpyDefault, cin)));
+    arrived[j] = pooled_event(n_ev++);
+    if (!copied || !arrived[j] || !ok(cudaEventRecord(arrived[j], cin))) return NV41_ERR_CUDA;
+  }
+
+  // own run in place, half before and half after the peers' slices: the first half hides the
+  // first copy-in, the second the last copy-out
+  int rc = own_run(o0, omid);
+  if (rc != NV41_OK) return rc;
+  for (size_t j = 0; j < slices.size(); ++j) {
+    const Slice& sl = slices[j];
+    if (!ok(cudaStreamWaitEvent(main, arrived[j], 0))) return NV41_ERR_CUDA;
+    void* y = at(s->y, sl.off * D * 2);
+    rc = experts(at(s->a_codes, sl.off * D), s->a_scale + sl.off, cap,
+                 w->ue8m0 ? at(s->a_atoms, sl.off / 128 * nkb * 512) : nullptr,
+                 s->a_weight + sl.off, s->a_tiles + sl.off / 128, sl.n, y);
+    if (rc != NV41_OK) return rc;
+    if (!order(main, cout) ||
+        !ok(cudaMemcpyAsync(at(peer_y[sl.g], sl.s0 * D * 2), y, static_cast<size_t>(sl.n) * D * 2,
+                            cudaMemcpyDefault, cout)))
+      return NV41_ERR_CUDA;
+  }
+  rc = own_run(omid, o1);
+  if (rc != NV41_OK) return rc;
+  // nothing later on the main stream starts before the side streams are done
+  if (!order(cin, main) || !order(cout, main)) return NV41_ERR_CUDA;
+  return NV41_OK;
+}

@@ -456,7 +456,7 @@ class SegContext(PeerBuffers):
 def moe_forward_fp8_seg(ctx: SegContext, x: torch.Tensor, wq_local: ops.Fp8ExpertWeights,
                         weights: torch.Tensor, indices: torch.Tensor, n_experts: int,
                         limit: float, shared: torch.Tensor | None = None,
-                        slice_rows: int = 65536) -> torch.Tensor:
+                        slice_rows: int = 65536, native: bool = True) -> torch.Tensor:
     """Expert-parallel forward in which no kernel moves rows between ranks.
 
     Same arguments and result as ``moe_forward_fp8_ep``.  The home rank quantises its tokens once
@@ -467,7 +467,10 @@ def moe_forward_fp8_seg(ctx: SegContext, x: torch.Tensor, wq_local: ops.Fp8Exper
     the bf16 results back into the home rank's ``y`` at the same rows on a second side stream.
     Its own run is used in place, split around the peers' slices.  One all-gather of G+2 integers per rank (host-read) gives
     the run boundaries and orders "peer's buffers are ready" before the copies; a one-word
-    all-reduce fences the results before the top-k sum."""
+    all-reduce fences the results before the top-k sum.
+
+    With ``native`` (default) the owner's side runs inside one library call
+    (nv41_ep_owner_forward); otherwise the same sequence is issued from here, call by call."""
     from dataclasses import replace
     world, me, dev = ctx.world, ctx.rank, ctx.dev
     T, D = x.shape
@@ -499,6 +502,10 @@ def moe_forward_fp8_seg(ctx: SegContext, x: torch.Tensor, wq_local: ops.Fp8Exper
     everyone = torch.empty((world, world + 2), dtype=torch.int32, device=dev)
     dist.all_gather_into_tensor(everyone, mine.contiguous(), group=ctx.group)
     B = everyone.tolist()                       # the one host synchronisation
+    if native:
+        _owner_forward_native(ctx, B, wq_local, limit, slice_rows)
+        ctx.fence()
+        return ops.combine(y_mine, lay.row_of_flat, T, k, shared)
 
     def experts(ac, asc, sf, w, tiles, out):
         n = ac.shape[0]
@@ -571,6 +578,52 @@ def moe_forward_fp8_seg(ctx: SegContext, x: torch.Tensor, wq_local: ops.Fp8Exper
         main.wait_event(joined)
     ctx.fence()                                  # every rank's results have landed
     return ops.combine(y_mine, lay.row_of_flat, T, k, shared)
+
+
+def _owner_forward_native(ctx: SegContext, B, wq: ops.Fp8ExpertWeights, limit: float,
+                          slice_rows: int) -> None:
+    """Scratch sized from the gathered bounds, then one nv41_ep_owner_forward call."""
+    import ctypes as C
+    from ._lib import EpScratch, EpWeights
+    world, me, dev, D = ctx.world, ctx.rank, ctx.dev, ctx.D
+    I = wq.w13_codes.shape[1] // 2
+    nkb = D // 128
+    slice_rows = max(128, slice_rows // 128 * 128)
+    remote = sum(B[g][me + 1] - B[g][me] for g in range(world) if g != me)
+    own = B[me][me + 1] - B[me][me]
+    half = max(own // 256 * 128, own - own // 256 * 128)
+    biggest = max([half] + [min(slice_rows, B[g][me + 1] - B[g][me]) for g in range(world) if g != me])
+    cap, hcap = max(remote, 128), max(biggest, 128)
+    u8 = dict(dtype=torch.uint8, device=dev)
+    a_codes = torch.empty(cap * D, **u8)
+    a_scale = torch.empty(nkb * cap, dtype=torch.float32, device=dev)
+    a_weight = torch.empty(cap, dtype=torch.float32, device=dev)
+    a_tiles = torch.empty(cap // 128, dtype=torch.int32, device=dev)
+    a_atoms = torch.empty(cap // 128 * nkb * 512, **u8) if wq.ue8m0 else None
+    y = torch.empty(cap * D, dtype=torch.bfloat16, device=dev)
+    h_codes = torch.empty(hcap * I, **u8)
+    h_scale = torch.empty(I // 128 * hcap, dtype=torch.float32, device=dev)
+    h_sf = torch.empty(hcap // 128 * (I // 128) * 512, **u8) if wq.ue8m0 else None
+    ptr = lambda t: None if t is None else t.data_ptr()
+    if wq.ue8m0:
+        w = EpWeights(ptr(wq.w13_codes), ptr(wq.w13_sf), ptr(wq.w2_codes), ptr(wq.w2_sf), 0, 0, 0,
+                      wq.E, I, D, 1, float(limit))
+    else:
+        w = EpWeights(ptr(wq.w13_codes), ptr(wq.w13_scale), ptr(wq.w2_codes), ptr(wq.w2_scale),
+                      wq.w2_scale.stride(0), wq.w2_scale.stride(1), wq.w2_scale.stride(2),
+                      wq.E, I, D, 0, float(limit))
+    sc = EpScratch(ptr(a_codes), ptr(a_scale), ptr(a_weight), ptr(a_tiles), ptr(a_atoms), ptr(y), cap,
+                   ptr(h_codes), ptr(h_scale), ptr(h_sf), hcap)
+    flat = [int(v) for row in B for v in row]
+    bounds = (C.c_longlong * len(flat))(*flat)
+    cin, cout = ctx.side_streams()
+    st = ops.status_word(dev)
+    ops.check(ctx._lib.nv41_ep_owner_forward(
+        bounds, world, me, slice_rows, ctx.addr_array("codes"), ctx.addr_array("scales"),
+        ctx.addr_array("weight"), ctx.addr_array("tiles"),
+        ctx.addr_array("atoms") if wq.ue8m0 else None, ctx.addr_array("y"), C.byref(w),
+        C.byref(sc), st.data_ptr(), ops._stream(), cin.cuda_stream, cout.cuda_stream),
+        "nv41_ep_owner_forward")
 
 
 def shard_expert_weights(w1, w3, w2, rank: int, world: int):

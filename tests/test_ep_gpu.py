@@ -69,9 +69,10 @@ def _worker(rank, world, port):
                 w1.contiguous(), w3.contiguous(), w2.contiguous(), ue8m0=True)
             wa = wq_all if not ue8m0 else ops.quantize_expert_weights(g["w1"], g["w3"], g["w2"],
                                                                       ue8m0=True)
-            for xs in (g["x"][sl], x2):
+            for xs, native in ((g["x"][sl], True), (x2, True), (x2, False)):
                 got = ep.moe_forward_fp8_seg(seg, xs, wl, g["weights"][sl], g["indices"][sl],
-                                             CASE["E"], 10.0, shared, slice_rows=128)
+                                             CASE["E"], 10.0, shared, slice_rows=128,
+                                             native=native)
                 want = ops.moe_forward_fp8(xs, wa, g["weights"][sl], g["indices"][sl], 10.0, shared)
                 ops.check_status()
                 assert torch.equal(got, want), ue8m0
