@@ -212,6 +212,22 @@ int nv41_moe_gemm_nvfp4(const void* a_packed, const void* a_sf, float a_global,
                         int N, int Kpad, const int* tile_expert, long long P_max, void* c_out,
                         long long c_ld, unsigned* status, void* stream);
 
+/* NVFP4 gate/up GEMM with the SwiGLU and the NVFP4 re-quantisation of h fused into the epilogue
+ * (nanov41/triton_grouped_moe.py:947-1043 _swiglu_fwd_* applied to the W4A4 operands of
+ * experiments/tl_kernels/nvfp4_gemm.py:165-241): gu = (A @ W13_e^T) * a_global * w13_global[e]
+ * rounded to bf16, h = bf16(w_row * silu(min(gate, L)) * clamp(up, -L, L)), h / h_global quantised
+ * in 16-element blocks -> h_packed [P_max, h_kpad/2] + scale atoms [P_max/128][h_kpad/64][512]
+ * (columns [I, h_kpad) are left untouched: zero them once).  Bit-identical to
+ * nv41_moe_gemm_nvfp4 -> nv41_swiglu_quant_nvfp4 without the bf16 gate|up round trip through
+ * HBM.  w13 rows per expert are INTERLEAVED in groups of 64: [W1[0:64]; W3[0:64]; W1[64:128];
+ * W3[64:128]; ...] (so one 128-row tile of B holds gate | up of 64 columns); I % 64 == 0,
+ * Kpad % 256 == 0, h_kpad % 256 == 0. */
+int nv41_moe_gemm1_nvfp4(const void* a_packed, const void* a_sf, float a_global,
+                         const void* w13_packed, const void* w13_sf, const float* w13_global,
+                         int E, int I, int Kpad, const int* tile_expert, const float* row_weight,
+                         long long P_max, float swiglu_limit, float h_global, void* h_packed,
+                         void* h_sf, int h_kpad, unsigned* status, void* stream);
+
 /* Expert-major copy of FP8 rows quantised once per token (the permute of
  * nanov41/fast_moe.py:399 / triton_grouped_moe.py:1507-1509 applied to codes and scales):
  * codes_rows[p] = codes[row_token[p]], scales_rows[kb][p] = scales[kb][row_token[p]]; padding

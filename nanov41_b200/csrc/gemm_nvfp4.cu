@@ -27,6 +27,7 @@
 #include <cstring>
 
 #include "../../include/nanov41_b200.h"
+#include "nvfp4_math.cuh"
 #include "ptx.cuh"
 #include "tmap.cuh"
 #include "util.cuh"
@@ -40,7 +41,8 @@ constexpr int kABytes = kTM * 128, kBBytes = kTN * 128;
 constexpr int kSfBytes = 4 * 512;                 // 4 k-groups x one 128-row atom
 constexpr int kStageBytes = kABytes + kBBytes + 2 * kSfBytes;   // 36 KiB
 constexpr int kStages = 5;
-constexpr int kThreads = 384;
+constexpr int kThreads = 384;            // plain store epilogue: 4 + 8 warps
+constexpr int kThreadsFused = 640;       // SwiGLU + NVFP4 epilogue: 4 + 16 warps
 constexpr int kSmemBytes = kStages * kStageBytes + (2 * kStages + 4) * 8 + 16 + 1024;
 constexpr uint32_t kColSfa = 256, kColSfb = 272;  // TMEM columns of the scale factors
 
@@ -56,7 +58,16 @@ struct Args {
   long long ld_out;
   int N, n_tiles_m, n_tiles_n, nstage, kgroups;   // kgroups = Kpad / 64
   uint32_t* status;
+  // fused SwiGLU + NVFP4 re-quantisation (EPI_SWIGLU_FP4): B rows come in 128-row groups of
+  // 64 gate rows then 64 up rows, so a tile holds gate | up of 64 columns of h
+  const float* row_weight;       // [P_max]
+  float limit, h_global;
+  uint8_t* h_packed;             // [P_max, h_kpad/2]
+  uint8_t* h_sf;                 // [P_max/128][h_kpad/64][512]
+  int h_kpad;
 };
+
+constexpr int EPI_STORE = 0, EPI_SWIGLU_FP4 = 1;
 
 struct Smem {
   uint8_t* base;
@@ -116,7 +127,9 @@ __device__ __forceinline__ void umma_nvfp4(uint32_t tmem_d, uint64_t adesc, uint
        w_ < total_; w_ += gridDim.x)                                                              \
     if ((mt = w_ / (g).n_tiles_n, nt = w_ - mt * (g).n_tiles_n, e = (g).tile_expert[mt]) >= 0)
 
-__global__ void __launch_bounds__(kThreads, 1) nvfp4_gemm_kernel(const __grid_constant__ Args g) {
+template <int EPI>
+__global__ void __launch_bounds__(EPI == EPI_SWIGLU_FP4 ? kThreadsFused : kThreads, 1)
+nvfp4_gemm_kernel(const __grid_constant__ Args g) {
   extern __shared__ uint8_t smem_raw[];
   Smem sm;
   sm.base = reinterpret_cast<uint8_t*>(
@@ -129,7 +142,7 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemm_kernel(const __grid_co
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(sm.tfull(b), 1u);
-      mbar_init(sm.tempty(b), 8u);
+      mbar_init(sm.tempty(b), EPI == EPI_SWIGLU_FP4 ? 16u : 8u);   // one arrival per epilogue warp
     }
     *sm.abort_flag() = 0u;
     fence_mbar_init();
@@ -209,11 +222,40 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemm_kernel(const __grid_co
     NV41_FP4_FOR_EACH_UNIT(g, mt, nt, e) {
       const float sc = g.a_global * g.b_global[e];
       const long long row = static_cast<long long>(mt) * kTM + q * 32 + lane;
-      const int n0 = nt * kTN + half * 64;
-      __nv_bfloat16* dst = g.out + row * g.ld_out + n0;
       const uint32_t b = nunit & 1u, tph = (nunit >> 1) & 1u;
       if (!mbar_wait<40>(sm.tfull(b), tph, sm.abort_flag(), g.status, ST_TIMEOUT_TMEM_FULL)) break;
       tc_fence_after_sync();
+      if (EPI == EPI_SWIGLU_FP4) {
+        // thread = (row, part): gate columns [16 part, +16) and up columns 64 + [16 part, +16)
+        // of the tile -> 16 values of h = one NVFP4 block (`half` runs over 0..3 here: sixteen
+        // epilogue warps).  gate / up are rounded to bf16 first (the dtype the unfused GEMM
+        // stores) so the result equals GEMM -> SwiGLU -> quantizer.
+        uint32_t gv[16], uv[16];
+        tmem_ld_32x32b_x16(lane_base + b * kTN + half * 16, gv);
+        tmem_ld_32x32b_x16(lane_base + b * kTN + 64 + half * 16, uv);
+        tmem_ld_wait_x16(gv);
+        tmem_ld_wait_x16(uv);
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(sm.tempty(b));     // accumulator is in registers
+        const float w = g.row_weight[row], L = g.limit;
+        const int blk = nt * 4 + half;                 // 16-element block index inside the h row
+        float f[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i)
+          f[i] = swiglu_h(__bfloat162float(__float2bfloat16_rn(__uint_as_float(gv[i]) * sc)),
+                          __bfloat162float(__float2bfloat16_rn(__uint_as_float(uv[i]) * sc)), w, L,
+                          g.h_global);
+        uint2 packed;
+        uint8_t sb;
+        nvfp4_block(f, packed, sb, g.h_global == 1.0f);
+        g.h_sf[sf_atom_offset(row, blk, g.h_kpad / 64)] = sb;
+        *reinterpret_cast<uint2*>(g.h_packed + row * (g.h_kpad / 2) + blk * 8) = packed;
+        ++nunit;
+        continue;
+      }
+      const int n0 = nt * kTN + half * 64;
+      __nv_bfloat16* dst = g.out + row * g.ld_out + n0;
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         uint32_t v[16];
@@ -255,18 +297,14 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemm_kernel(const __grid_co
 
 using namespace nv41;
 
-extern "C" int nv41_moe_gemm_nvfp4(const void* a_packed, const void* a_sf, float a_global,
-                                   const void* b_packed, const void* b_sf, const float* b_global,
-                                   int E, int N, int Kpad, const int* tile_expert,
-                                   long long P_max, void* c_out, long long c_ld, unsigned* status,
-                                   void* stream) {
-  if (!a_packed || !a_sf || !b_packed || !b_sf || !b_global || !tile_expert || !c_out || !status)
+static int launch_nvfp4(fp4::Args& g, int epi, const void* a_packed, const void* a_sf,
+                        float a_global, const void* b_packed, const void* b_sf,
+                        const float* b_global, int E, int N, int Kpad, const int* tile_expert,
+                        long long P_max, unsigned* status, void* stream) {
+  if (!a_packed || !a_sf || !b_packed || !b_sf || !b_global || !tile_expert || !status)
     return NV41_ERR_INVALID;
-  if (E <= 0 || N <= 0 || Kpad <= 0 || P_max <= 0 || (P_max % 128) != 0 || c_ld < N)
-    return NV41_ERR_INVALID;
-  if ((Kpad % 256) != 0 || (N % 128) != 0 || (c_ld % 8) != 0) return NV41_ERR_UNSUPPORTED;
-  fp4::Args g;
-  memset(&g, 0, sizeof(g));
+  if (E <= 0 || N <= 0 || Kpad <= 0 || P_max <= 0 || (P_max % 128) != 0) return NV41_ERR_INVALID;
+  if ((Kpad % 256) != 0 || (N % 128) != 0) return NV41_ERR_UNSUPPORTED;
   int rc = make_tmap_2d(&g.tmap_a, a_packed, static_cast<unsigned long long>(P_max), Kpad / 2, 1,
                         128, 128);
   if (rc != NV41_OK) return rc;
@@ -278,25 +316,61 @@ extern "C" int nv41_moe_gemm_nvfp4(const void* a_packed, const void* a_sf, float
   g.tile_expert = tile_expert;
   g.b_global = b_global;
   g.a_global = a_global;
-  g.out = static_cast<__nv_bfloat16*>(c_out);
-  g.ld_out = c_ld;
   g.N = N;
   g.n_tiles_m = static_cast<int>(P_max / 128);
   g.n_tiles_n = N / fp4::kTN;
   g.nstage = Kpad / fp4::kStageK;
   g.kgroups = Kpad / 64;
   g.status = status;
-  static bool configured = false;
-  if (!configured) {
-    if (cudaFuncSetAttribute(fp4::nvfp4_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+  auto* kern = epi == fp4::EPI_SWIGLU_FP4 ? fp4::nvfp4_gemm_kernel<fp4::EPI_SWIGLU_FP4>
+                                          : fp4::nvfp4_gemm_kernel<fp4::EPI_STORE>;
+  static bool configured[2] = {false, false};
+  if (!configured[epi]) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              fp4::kSmemBytes) != cudaSuccess)
       return NV41_ERR_CUDA;
-    configured = true;
+    configured[epi] = true;
   }
   const long long units = static_cast<long long>(g.n_tiles_m) * g.n_tiles_n;
   int grid = persistent_grid(sm_count());
   if (units < grid) grid = static_cast<int>(units);
-  fp4::nvfp4_gemm_kernel<<<grid, fp4::kThreads, fp4::kSmemBytes,
-                           static_cast<cudaStream_t>(stream)>>>(g);
+  kern<<<grid, epi == fp4::EPI_SWIGLU_FP4 ? fp4::kThreadsFused : fp4::kThreads, fp4::kSmemBytes,
+         static_cast<cudaStream_t>(stream)>>>(g);
   return launch_status();
+}
+
+extern "C" int nv41_moe_gemm_nvfp4(const void* a_packed, const void* a_sf, float a_global,
+                                   const void* b_packed, const void* b_sf, const float* b_global,
+                                   int E, int N, int Kpad, const int* tile_expert,
+                                   long long P_max, void* c_out, long long c_ld, unsigned* status,
+                                   void* stream) {
+  if (!c_out || c_ld < N) return NV41_ERR_INVALID;
+  if ((c_ld % 8) != 0) return NV41_ERR_UNSUPPORTED;
+  fp4::Args g;
+  memset(&g, 0, sizeof(g));
+  g.out = static_cast<__nv_bfloat16*>(c_out);
+  g.ld_out = c_ld;
+  return launch_nvfp4(g, fp4::EPI_STORE, a_packed, a_sf, a_global, b_packed, b_sf, b_global, E, N,
+                      Kpad, tile_expert, P_max, status, stream);
+}
+
+extern "C" int nv41_moe_gemm1_nvfp4(const void* a_packed, const void* a_sf, float a_global,
+                                    const void* w13_packed, const void* w13_sf,
+                                    const float* w13_global, int E, int I, int Kpad,
+                                    const int* tile_expert, const float* row_weight,
+                                    long long P_max, float swiglu_limit, float h_global,
+                                    void* h_packed, void* h_sf, int h_kpad, unsigned* status,
+                                    void* stream) {
+  if (!row_weight || !h_packed || !h_sf || I <= 0 || !(h_global > 0.f)) return NV41_ERR_INVALID;
+  if ((I % 64) != 0 || h_kpad < I || (h_kpad % 256) != 0) return NV41_ERR_UNSUPPORTED;
+  fp4::Args g;
+  memset(&g, 0, sizeof(g));
+  g.row_weight = row_weight;
+  g.limit = swiglu_limit;
+  g.h_global = h_global;
+  g.h_packed = static_cast<uint8_t*>(h_packed);
+  g.h_sf = static_cast<uint8_t*>(h_sf);
+  g.h_kpad = h_kpad;
+  return launch_nvfp4(g, fp4::EPI_SWIGLU_FP4, a_packed, a_sf, a_global, w13_packed, w13_sf,
+                      w13_global, E, 2 * I, Kpad, tile_expert, P_max, status, stream);
 }

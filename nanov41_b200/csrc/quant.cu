@@ -17,6 +17,7 @@
 
 #include "../../include/nanov41_b200.h"
 #include "quant_math.cuh"
+#include "nvfp4_math.cuh"
 #include "util.cuh"
 
 namespace nv41 {
@@ -238,17 +239,6 @@ quant_fp8_128x128_kernel(const __nv_bfloat16* __restrict__ w, int E, int N, int 
   }
 }
 
-// ------------------------------------------------------------------------- NVFP4 1x16 blocks
-// One lane per 16-element block.  code = (#boundaries strictly below min(|q|, 6)) with
-// boundaries {0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5}  (ties go toward zero), +8 when the value is
-// negative and the magnitude index is non-zero.  Packed low nibble = even column.
-__device__ __forceinline__ uint32_t e2m1_code(float q) {
-  const float a = fminf(fabsf(q), 6.0f);
-  uint32_t idx = (a > 0.25f) + (a > 0.75f) + (a > 1.25f) + (a > 1.75f) + (a > 2.5f) +
-                 (a > 3.5f) + (a > 5.0f);
-  return idx | ((q < 0.f && idx != 0u) ? 8u : 0u);
-}
-
 template <bool kInputFp32>
 __global__ void __launch_bounds__(256)
 quant_nvfp4_1x16_kernel(const void* __restrict__ xin, long long rows, int K, float global_scale,
@@ -307,48 +297,6 @@ quant_nvfp4_1x16_kernel(const void* __restrict__ xin, long long rows, int K, flo
 // K padded to 256 (zero codes, zero scale bytes), rows optionally gathered (row index -1 = zero
 // row), and the e4m3 scale bytes written in 512-byte atoms
 //   sf[(row / 128) * (Kpad / 64) + k / 64][(row % 32) * 16 + (row / 32 % 4) * 4 + (k / 16) % 4].
-__device__ __forceinline__ long long sf_atom_offset(long long row, int blk16, int kgroups) {
-  return ((row >> 7) * kgroups + (blk16 >> 2)) * 512 + (row & 31) * 16 + ((row >> 5) & 3) * 4 +
-         (blk16 & 3);
-}
-
-// `bf16_values`: the 16 inputs are bf16 numbers (8 significant bits) that were not divided by a
-// global scale.  Then |f / s| > b  <=>  |f| > b * s exactly (b * s has at most 7 significant
-// bits, so a quotient can never round onto a boundary from above), and the codes follow from
-// seven products instead of sixteen IEEE divisions.
-__device__ __forceinline__ void nvfp4_block(const float (&f)[16], uint2& packed, uint8_t& sbyte,
-                                            bool bf16_values = false) {
-  float amax = 0.f;
-#pragma unroll
-  for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(f[i]));
-  amax = fmaxf(amax, 1e-8f);
-  const __nv_fp8_storage_t sb =
-      __nv_cvt_float_to_fp8(__fdiv_rn(amax, 6.0f), __NV_SATFINITE, __NV_E4M3);
-  const __half_raw hr = __nv_cvt_fp8_to_halfraw(sb, __NV_E4M3);
-  float s = __half2float(__half(hr));
-  s = fmaxf(s, 0.001953125f);
-  uint32_t words[2] = {0u, 0u};
-  if (bf16_values) {
-    const float t0 = 0.25f * s, t1 = 0.75f * s, t2 = 1.25f * s, t3 = 1.75f * s, t4 = 2.5f * s,
-                t5 = 3.5f * s, t6 = 5.0f * s;
-#pragma unroll
-    for (int i = 0; i < 16; ++i) {
-      const float a = fabsf(f[i]);
-      const uint32_t idx = (a > t0) + (a > t1) + (a > t2) + (a > t3) + (a > t4) + (a > t5) + (a > t6);
-      const uint32_t c = idx | ((f[i] < 0.f && idx != 0u) ? 8u : 0u);
-      words[i >> 3] |= c << (4 * (i & 7));
-    }
-  } else {
-#pragma unroll
-    for (int i = 0; i < 16; ++i) {
-      const uint32_t c = e2m1_code(__fdiv_rn(f[i], s));
-      words[i >> 3] |= c << (4 * (i & 7));
-    }
-  }
-  packed = make_uint2(words[0], words[1]);
-  sbyte = (s == 0.001953125f) ? static_cast<uint8_t>(0x01) : static_cast<uint8_t>(sb);
-}
-
 template <bool kInputFp32>
 __global__ void __launch_bounds__(256)
 quant_nvfp4_tc_kernel(const void* __restrict__ xin, long long ld_x, const int* __restrict__ gather,
@@ -428,17 +376,7 @@ swiglu_quant_nvfp4_kernel(const __nv_bfloat16* __restrict__ gu, const float* __r
         for (int i = 0; i < 8; ++i) { u[i] = lo[i]; u[8 + i] = hi[i]; }
       }
 #pragma unroll
-      for (int i = 0; i < 16; ++i) {
-        float gt = g[i], up = u[i];
-        if (L > 0.f) {
-          up = fminf(fmaxf(up, -L), L);
-          gt = fminf(gt, L);
-        }
-        const float sl = gt / (1.f + __expf(-gt));
-        float h = __bfloat162float(__float2bfloat16_rn((sl * up) * w));
-        if (global_scale != 1.0f) h = __fdiv_rn(h, global_scale);
-        f[i] = h;
-      }
+      for (int i = 0; i < 16; ++i) f[i] = swiglu_h(g[i], u[i], w, L, global_scale);
       nvfp4_block(f, out, sb, global_scale == 1.0f);
     }
     *reinterpret_cast<uint2*>(packed + row * (Ipad / 2) + blk * 8) = out;

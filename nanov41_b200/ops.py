@@ -548,6 +548,7 @@ class Nvfp4ExpertWeights:
     E: int
     I: int
     D: int
+    interleaved: bool = False  # w13 rows in 64-row groups gate | up (for the fused gate/up GEMM)
 
 
 def nvfp4_global_scale(w: torch.Tensor) -> float:
@@ -556,11 +557,19 @@ def nvfp4_global_scale(w: torch.Tensor) -> float:
 
 
 def quantize_expert_weights_nvfp4(w1, w3, w2, g13: float | None = None,
-                                  g2: float | None = None) -> Nvfp4ExpertWeights:
+                                  g2: float | None = None,
+                                  interleave: bool = True) -> Nvfp4ExpertWeights:
     """w1, w3: bf16 [E, I, D]; w2: bf16 [E, D, I].  One-off preparation (reads the tensor
-    maxima on the host unless the global scales are given)."""
+    maxima on the host unless the global scales are given).  With ``interleave`` (needs
+    I % 64 == 0) the rows of W13 are stored [W1[0:64]; W3[0:64]; W1[64:128]; ...] per expert, the
+    order the fused gate/up GEMM reads; otherwise [W1; W3]."""
     E, I, D = w1.shape
-    w13 = torch.cat((w1, w3), dim=1).reshape(E * 2 * I, D).contiguous()
+    interleave = interleave and I % 64 == 0
+    if interleave:
+        w13 = torch.cat((w1.reshape(E, I // 64, 64, D), w3.reshape(E, I // 64, 64, D)), dim=2)
+        w13 = w13.reshape(E * 2 * I, D).contiguous()
+    else:
+        w13 = torch.cat((w1, w3), dim=1).reshape(E * 2 * I, D).contiguous()
     w2f = w2.reshape(E * D, I).contiguous()
     g13 = nvfp4_global_scale(w13) if g13 is None else g13
     g2 = nvfp4_global_scale(w2f) if g2 is None else g2
@@ -569,7 +578,7 @@ def quantize_expert_weights_nvfp4(w1, w3, w2, g13: float | None = None,
     dev = w1.device
     return Nvfp4ExpertWeights(p13, s13, torch.full((E,), g13, dtype=torch.float32, device=dev),
                               p2, s2, torch.full((E,), g2, dtype=torch.float32, device=dev),
-                              E, I, D)
+                              E, I, D, interleave)
 
 
 def gemm_nvfp4(a_packed, a_sf, a_global: float, b_packed, b_sf, b_global, E: int, N: int,
@@ -587,6 +596,30 @@ def gemm_nvfp4(a_packed, a_sf, a_global: float, b_packed, b_sf, b_global, E: int
                                           out.stride(0), _ptr(st), _stream()),
           "nv41_moe_gemm_nvfp4")
     return out
+
+
+def gemm1_nvfp4(a_packed, a_sf, a_global: float, wq: Nvfp4ExpertWeights, layout: DeviceLayout,
+                limit: float, h_global: float = 1.0):
+    """Gate/up NVFP4 GEMM + SwiGLU + NVFP4 re-quantisation of h in one kernel -> (h_packed
+    [P_max, Ipad/2], h scale atoms); ``wq`` must hold interleaved W13 rows."""
+    _need_cuda(a_packed, a_sf)
+    if not wq.interleaved:
+        raise Nv41Error("gemm1_nvfp4 needs weights quantised with interleave=True")
+    kpad = a_packed.shape[1] * 2
+    P = layout.P_max
+    ipad = ceil_to(wq.I, 256)
+    dev = a_packed.device
+    alloc = torch.zeros if ipad != wq.I else torch.empty
+    packed = alloc((P, ipad // 2), dtype=torch.uint8, device=dev)
+    sf = alloc(P // 128 * (ipad // 64) * 512, dtype=torch.uint8, device=dev)
+    st = status_word(dev)
+    check(_lib.load().nv41_moe_gemm1_nvfp4(_ptr(a_packed), _ptr(a_sf), float(a_global),
+                                           _ptr(wq.w13_packed), _ptr(wq.w13_sf),
+                                           _ptr(wq.w13_global), wq.E, wq.I, kpad,
+                                           _ptr(layout.tile_expert), _ptr(layout.row_weight), P,
+                                           float(limit), float(h_global), _ptr(packed), _ptr(sf),
+                                           ipad, _ptr(st), _stream()), "nv41_moe_gemm1_nvfp4")
+    return packed, sf
 
 
 def swiglu_quant_nvfp4(gu: torch.Tensor, layout: DeviceLayout, limit: float,
@@ -618,9 +651,13 @@ def moe_forward_nvfp4(x, wq: Nvfp4ExpertWeights, weights, indices, limit: float,
     if layout is None:
         layout = build_layout(indices.reshape(-1), wq.E, k, weights.reshape(-1))
     xp, xsf = quant_nvfp4_tc(x.contiguous(), x_global, gather=layout.row_token)
-    gu = gemm_nvfp4(xp, xsf, x_global, wq.w13_packed, wq.w13_sf, wq.w13_global, wq.E, 2 * wq.I,
-                    layout)
-    hp, hsf = swiglu_quant_nvfp4(gu, layout, limit, h_global)
+    gu = None
+    if wq.interleaved:
+        hp, hsf = gemm1_nvfp4(xp, xsf, x_global, wq, layout, limit, h_global)
+    else:
+        gu = gemm_nvfp4(xp, xsf, x_global, wq.w13_packed, wq.w13_sf, wq.w13_global, wq.E,
+                        2 * wq.I, layout)
+        hp, hsf = swiglu_quant_nvfp4(gu, layout, limit, h_global)
     y_rows = gemm_nvfp4(hp, hsf, h_global, wq.w2_packed, wq.w2_sf, wq.w2_global, wq.E, wq.D, layout)
     out = combine(y_rows, layout.row_of_flat, T, k, shared)
     if return_parts:

@@ -76,11 +76,23 @@ def test_forward_nvfp4_vs_oracle(case):
     from nanov41_b200 import ops
     c = make_case(seed=7, outliers=False, **case)
     g = {n: t.cuda() for n, t in c.items()}
-    wq = ops.quantize_expert_weights_nvfp4(g["w1"], g["w3"], g["w2"])
+    wq = ops.quantize_expert_weights_nvfp4(g["w1"], g["w3"], g["w2"], interleave=False)
     g13, g2 = float(wq.w13_global[0]), float(wq.w2_global[0])
     out, parts = ops.moe_forward_nvfp4(g["x"], wq, g["weights"], g["indices"], LIMIT,
                                        return_parts=True)
     ops.check_status()
+    # the fused gate/up kernel (SwiGLU + NVFP4 re-quantisation in the GEMM epilogue, interleaved
+    # W13 rows) must reproduce GEMM -> SwiGLU -> quantizer bit for bit
+    wf = ops.quantize_expert_weights_nvfp4(g["w1"], g["w3"], g["w2"])
+    assert wf.interleaved
+    out_f, parts_f = ops.moe_forward_nvfp4(g["x"], wf, g["weights"], g["indices"], LIMIT,
+                                           return_parts=True)
+    ops.check_status()
+    used = int(parts["layout"].meta[1])
+    assert torch.equal(parts_f["h_packed"][:used], parts["h_packed"][:used])
+    n_sf = used // 128 * (parts["h_packed"].shape[1] * 2 // 64) * 512
+    assert torch.equal(parts_f["h_sf"][:n_sf], parts["h_sf"][:n_sf])
+    assert torch.equal(out_f, out)
     ref, rp = OM.moe_nvfp4(c["x"], c["w1"], c["w3"], c["w2"], c["weights"], c["indices"], LIMIT,
                            g13, g2, return_parts=True)
     pad_pos = parts["layout"].pad_pos.cpu().long()
