@@ -479,8 +479,8 @@ def run_ours(args):
         w4 = ops.quantize_expert_weights_nvfp4(*w_bf16)
         ms = timed(lambda: ops.moe_forward_nvfp4(g["x"], w4, g["weights"], g["indices"], LIMIT),
                    args.steps, args.warmup)
-        xp, xsf = ops.quant_nvfp4_tc(g["x"], 1.0, gather=lay.row_token)
-        f0 = lambda: ops.quant_nvfp4_tc(g["x"], 1.0, gather=lay.row_token)
+        xp, xsf = ops.gather_nvfp4_rows(*ops.quant_nvfp4_tc(g["x"], 1.0), lay)
+        f0 = lambda: ops.gather_nvfp4_rows(*ops.quant_nvfp4_tc(g["x"], 1.0), lay)
         f1 = lambda: ops.gemm1_nvfp4(xp, xsf, 1.0, w4, lay, LIMIT)    # SwiGLU + re-quant fused
         hp, hsf = f1()
         f2 = lambda: ops.gemm_nvfp4(hp, hsf, 1.0, w4.w2_packed, w4.w2_sf, w4.w2_global, E, D, lay)

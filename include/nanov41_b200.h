@@ -228,6 +228,16 @@ int nv41_moe_gemm1_nvfp4(const void* a_packed, const void* a_sf, float a_global,
                          long long P_max, float swiglu_limit, float h_global, void* h_packed,
                          void* h_sf, int h_kpad, unsigned* status, void* stream);
 
+/* Expert-major copy of NVFP4 rows quantised once per token with nv41_quant_nvfp4_tc (the permute
+ * of nanov41/fast_moe.py:399 / triton_grouped_moe.py:1507-1509 applied to packed codes and scale
+ * atoms): packed_rows[p] = packed[row_token[p]] ([., Kpad/2] bytes) and the row's scale bytes moved
+ * to the padded row's place in the atoms [P_max/128][Kpad/64][512]; padding rows get zero codes
+ * and the scale bytes of an all-zero row (0x01 inside K).  Rows past meta[1] are not written.
+ * Kpad % 256 == 0, Kpad >= K. */
+int nv41_gather_nvfp4_rows(const void* packed, const void* sf_atoms, const int* row_token,
+                           const int* meta, int K, int Kpad, long long P_max, void* packed_rows,
+                           void* sf_rows, void* stream);
+
 /* Expert-major copy of FP8 rows quantised once per token (the permute of
  * nanov41/fast_moe.py:399 / triton_grouped_moe.py:1507-1509 applied to codes and scales):
  * codes_rows[p] = codes[row_token[p]], scales_rows[kb][p] = scales[kb][row_token[p]]; padding

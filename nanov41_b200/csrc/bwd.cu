@@ -72,6 +72,43 @@ gather_fp8_rows_kernel(const uint8_t* __restrict__ codes, long long ld, const fl
   }
 }
 
+// Expert-major copy of per-token NVFP4 rows (quantised once per token): packed_rows[p] =
+// packed[row_token[p]] and the row's e4m3 scale bytes moved from the token's position in the
+// 512-byte scale atoms to the padded row's (four bytes = one 64-element group at a time);
+// padding rows get what the quantizer gives an all-zero row.  One warp per padded row.
+__global__ void __launch_bounds__(256)
+gather_nvfp4_rows_kernel(const uint8_t* __restrict__ packed, const uint8_t* __restrict__ sf,
+                         const int* __restrict__ row_token, const int* __restrict__ meta,
+                         int K, int Kpad, uint8_t* __restrict__ packed_rows,
+                         uint8_t* __restrict__ sf_rows) {
+  const int lane = threadIdx.x & 31;
+  const long long warp0 = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const long long nwarps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
+  const long long used = meta[1];
+  const int kgroups = Kpad / 64, chunks = Kpad / 32;     // 16-byte chunks of Kpad/2 bytes
+  for (long long p = warp0; p < used; p += nwarps) {
+    const long long tok = row_token[p];
+    for (int c = lane; c < chunks; c += 32) {
+      uint4 v = make_uint4(0u, 0u, 0u, 0u);
+      if (tok >= 0) v = __ldg(reinterpret_cast<const uint4*>(packed + tok * (Kpad / 2)) + c);
+      reinterpret_cast<uint4*>(packed_rows + p * (Kpad / 2))[c] = v;
+    }
+    for (int kg = lane; kg < kgroups; kg += 32) {
+      // a padding row reads as an all-zero row put through the quantizer: scale byte 0x01 (the
+      // clamped minimum 2^-9) for blocks inside K, 0 in the K padding
+      uint32_t w = 0u;
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        if ((kg * 4 + j) * 16 < K) w |= 1u << (8 * j);
+      if (tok >= 0)
+        w = __ldg(reinterpret_cast<const uint32_t*>(
+            sf + ((tok >> 7) * kgroups + kg) * 512 + (tok & 31) * 16 + ((tok >> 5) & 3) * 4));
+      *reinterpret_cast<uint32_t*>(sf_rows + ((p >> 7) * kgroups + kg) * 512 + (p & 31) * 16 +
+                                   ((p >> 5) & 3) * 4) = w;
+    }
+  }
+}
+
 __device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
   const uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
@@ -211,6 +248,22 @@ extern "C" int nv41_gather_fp8_rows(const void* codes, long long ld, const float
   gather_fp8_rows_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const uint8_t*>(codes), ld, scales_kmajor, scale_kb_stride, row_token, meta, K,
       static_cast<uint8_t*>(codes_rows), scales_rows_kmajor, P_max, static_cast<uint8_t*>(sf_atoms));
+  return launch_status();
+}
+
+extern "C" int nv41_gather_nvfp4_rows(const void* packed, const void* sf_atoms,
+                                      const int* row_token, const int* meta, int K, int Kpad,
+                                      long long P_max, void* packed_rows, void* sf_rows,
+                                      void* stream) {
+  if (!packed || !sf_atoms || !row_token || !meta || !packed_rows || !sf_rows || K <= 0 ||
+      Kpad < K || (Kpad % 256) != 0 || P_max <= 0 || (P_max % 128) != 0)
+    return NV41_ERR_INVALID;
+  long long blocks = (P_max + 7) / 8;
+  if (blocks > 148LL * 16) blocks = 148LL * 16;
+  gather_nvfp4_rows_kernel<<<static_cast<unsigned>(blocks), 256, 0,
+                             static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint8_t*>(packed), static_cast<const uint8_t*>(sf_atoms), row_token, meta,
+      K, Kpad, static_cast<uint8_t*>(packed_rows), static_cast<uint8_t*>(sf_rows));
   return launch_status();
 }
 

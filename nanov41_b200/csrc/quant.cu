@@ -297,22 +297,27 @@ quant_nvfp4_1x16_kernel(const void* __restrict__ xin, long long rows, int K, flo
 // K padded to 256 (zero codes, zero scale bytes), rows optionally gathered (row index -1 = zero
 // row), and the e4m3 scale bytes written in 512-byte atoms
 //   sf[(row / 128) * (Kpad / 64) + k / 64][(row % 32) * 16 + (row / 32 % 4) * 4 + (k / 16) % 4].
+// One thread per 16-element block.  The launch makes the thread count a multiple of the blocks
+// per row, so a thread keeps its block column and walks down the rows (no division in the loop);
+// the four scale bytes of a 64-element group are gathered by shuffles and stored as one word.
 template <bool kInputFp32>
 __global__ void __launch_bounds__(256)
 quant_nvfp4_tc_kernel(const void* __restrict__ xin, long long ld_x, const int* __restrict__ gather,
                       long long rows, int K, int Kpad, float global_scale,
                       uint8_t* __restrict__ packed, uint8_t* __restrict__ sf) {
-  const int nblk = Kpad / 16, kgroups = Kpad / 64;
-  const long long n_items = rows * nblk;
-  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
-  for (long long item = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
-       item < n_items; item += stride) {
-    const long long row = item / nblk;
-    const int blk = static_cast<int>(item - row * nblk);
-    const long long src = gather ? static_cast<long long>(gather[row]) : row;
+  const int nblk = Kpad / 16, kgroups = Kpad / 64;     // nblk % 16 == 0 (Kpad % 256 == 0)
+  const unsigned tid = blockIdx.x * blockDim.x + threadIdx.x;
+  const unsigned nthreads = gridDim.x * blockDim.x;    // a multiple of nblk (see the launch)
+  const int blk = static_cast<int>(tid % nblk);
+  const long long row_step = nthreads / nblk;
+  const bool in_k = blk * 16 < K;
+  for (long long row = tid / nblk;; row += row_step) {
+    const bool active = row < rows;              // a warp may span two rows: keep it together
+    if (!__any_sync(0xFFFFFFFFu, active)) break;
+    const long long src = !active ? -1 : (gather ? static_cast<long long>(__ldg(gather + row)) : row);
     uint2 out = make_uint2(0u, 0u);
     uint8_t sb = 0;
-    if (blk * 16 < K) {
+    if (in_k && active) {
       float f[16];
 #pragma unroll
       for (int i = 0; i < 16; ++i) f[i] = 0.f;
@@ -328,9 +333,10 @@ quant_nvfp4_tc_kernel(const void* __restrict__ xin, long long ld_x, const int* _
         } else {
           const uint4* p = reinterpret_cast<const uint4*>(
               reinterpret_cast<const __nv_bfloat16*>(xin) + src * ld_x + blk * 16);
+          const uint4 v0 = __ldg(p), v1 = __ldg(p + 1);
           float lo[8], hi[8];
-          unpack_bf16x8(__ldg(p), lo);
-          unpack_bf16x8(__ldg(p + 1), hi);
+          unpack_bf16x8(v0, lo);
+          unpack_bf16x8(v1, hi);
 #pragma unroll
           for (int i = 0; i < 8; ++i) { f[i] = lo[i]; f[8 + i] = hi[i]; }
         }
@@ -341,8 +347,15 @@ quant_nvfp4_tc_kernel(const void* __restrict__ xin, long long ld_x, const int* _
       }
       nvfp4_block(f, out, sb, !kInputFp32 && global_scale == 1.0f);
     }
-    *reinterpret_cast<uint2*>(packed + row * (Kpad / 2) + blk * 8) = out;
-    sf[sf_atom_offset(row, blk, kgroups)] = sb;
+    if (active) *reinterpret_cast<uint2*>(packed + row * (Kpad / 2) + blk * 8) = out;
+    // lanes 4j .. 4j+3 hold the four blocks of one 64-element group of this row (the warp's 32
+    // consecutive threads are consecutive blocks, and nblk is a multiple of 16)
+    const uint32_t b0 = sb;
+    uint32_t word = b0 | (__shfl_down_sync(0xFFFFFFFFu, b0, 1) << 8) |
+                    (__shfl_down_sync(0xFFFFFFFFu, b0, 2) << 16) |
+                    (__shfl_down_sync(0xFFFFFFFFu, b0, 3) << 24);
+    if (active && (blk & 3) == 0)
+      *reinterpret_cast<uint32_t*>(sf + sf_atom_offset(row, blk, kgroups)) = word;
   }
 }
 
@@ -457,9 +470,11 @@ extern "C" int nv41_quant_nvfp4_tc(const void* x, int x_is_fp32, long long ld_x,
       (ld_x % 8) != 0 || !(global_scale > 0.f))
     return NV41_ERR_INVALID;
   const int Kpad = (K + 255) / 256 * 256;
-  const long long items = rows * (Kpad / 16);
+  const int nblk = Kpad / 16;
+  const long long items = rows * nblk;
   long long blocks = (items + 255) / 256;
-  if (blocks > 148LL * 64) blocks = 148LL * 64;
+  if (blocks > 148LL * 32) blocks = 148LL * 32;
+  blocks = (blocks + nblk - 1) / nblk * nblk;       // threads a multiple of the blocks per row
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (x_is_fp32)
     quant_nvfp4_tc_kernel<true><<<static_cast<unsigned>(blocks), 256, 0, st>>>(

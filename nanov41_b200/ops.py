@@ -536,6 +536,22 @@ def quant_nvfp4_tc(x: torch.Tensor, global_scale: float = 1.0, gather: torch.Ten
     return packed, sf
 
 
+def gather_nvfp4_rows(packed: torch.Tensor, sf: torch.Tensor, layout: DeviceLayout,
+                      K: int | None = None):
+    """Per-token NVFP4 rows (from ``quant_nvfp4_tc``) -> padded expert-major order: (packed
+    [P_max, Kpad/2], scale atoms).  ``K``: unpadded row length (default Kpad)."""
+    _need_cuda(packed, sf)
+    kpad = packed.shape[1] * 2
+    P = layout.P_max
+    out = torch.empty((P, kpad // 2), dtype=torch.uint8, device=packed.device)
+    sf_rows = torch.empty(P // 128 * (kpad // 64) * 512, dtype=torch.uint8, device=packed.device)
+    check(_lib.load().nv41_gather_nvfp4_rows(_ptr(packed), _ptr(sf), _ptr(layout.row_token),
+                                             _ptr(layout.meta), kpad if K is None else K, kpad, P,
+                                             _ptr(out), _ptr(sf_rows),
+                                             _stream()), "nv41_gather_nvfp4_rows")
+    return out, sf_rows
+
+
 @dataclass
 class Nvfp4ExpertWeights:
     """NVFP4 expert weights: packed e2m1 + e4m3 scale atoms + one fp32 global scale per tensor."""
@@ -650,7 +666,8 @@ def moe_forward_nvfp4(x, wq: Nvfp4ExpertWeights, weights, indices, limit: float,
     k = indices.shape[1]
     if layout is None:
         layout = build_layout(indices.reshape(-1), wq.E, k, weights.reshape(-1))
-    xp, xsf = quant_nvfp4_tc(x.contiguous(), x_global, gather=layout.row_token)
+    xq, xq_sf = quant_nvfp4_tc(x.contiguous(), x_global)          # once per token
+    xp, xsf = gather_nvfp4_rows(xq, xq_sf, layout, D)             # then permuted as bytes
     gu = None
     if wq.interleaved:
         hp, hsf = gemm1_nvfp4(xp, xsf, x_global, wq, layout, limit, h_global)

@@ -102,3 +102,17 @@ def test_forward_nvfp4_vs_oracle(case):
     assert mx <= 2e-2 and mean <= 2e-3, ("y_rows", mx, mean)
     mx, mean = OM.rel_errors(out.cpu(), ref)
     assert mx <= 2e-2 and mean <= 2e-3, ("out", mx, mean)
+
+
+def test_gather_of_quantised_rows_equals_quantised_gather():
+    """Quantise once per token, then permute bytes == permute, then quantise every routed row."""
+    from nanov41_b200 import ops
+    c = make_case(seed=9, T=600, E=8, k=2, D=320, I=128, empty_expert=5)
+    g = {n: t.cuda() for n, t in c.items()}
+    lay = ops.build_layout(g["indices"].reshape(-1), 8, 2, g["weights"].reshape(-1))
+    want_p, want_sf = ops.quant_nvfp4_tc(g["x"], 1.0, gather=lay.row_token)
+    got_p, got_sf = ops.gather_nvfp4_rows(*ops.quant_nvfp4_tc(g["x"], 1.0), lay, 320)
+    used = int(lay.meta[1])
+    n_sf = used // 128 * (want_p.shape[1] * 2 // 64) * 512
+    assert torch.equal(got_p[:used], want_p[:used])
+    assert torch.equal(got_sf[:n_sf], want_sf[:n_sf])
