@@ -36,6 +36,53 @@ SPEC_FP8_TFLOPS = 4500.0
 
 
 # ------------------------------------------------------------------------------ clocks
+class PipelinedE2E:
+    """End-to-end step with the transfers off the compute stream: every step copies its inputs
+    from pinned host memory (copy-in stream), runs ``forward`` on the current stream, and copies
+    the result back to pinned host memory (copy-out stream).  Two sets of device / host buffers
+    alternate, so the host->device copy of step i+1 and the device->host copy of step i-1 overlap
+    the kernels of step i.  ``finish()`` makes the current stream wait for both side streams, so
+    an event recorded after it covers every copy."""
+
+    def __init__(self, host_inputs, forward, out_shape, dev):
+        self.host_inputs, self.forward, self.dev = host_inputs, forward, dev
+        self.s_in, self.s_out = torch.cuda.Stream(), torch.cuda.Stream()
+        self.dev_inputs = [[torch.empty_like(h, device=dev) for h in host_inputs] for _ in range(2)]
+        self.out_host = [torch.empty(out_shape, dtype=torch.bfloat16).pin_memory() for _ in range(2)]
+        self.consumed = [None, None]     # compute has read input set j
+        self.copied_out = [None, None]   # result j is in host memory
+        self.i = 0
+
+    def __call__(self):
+        j, main = self.i & 1, torch.cuda.current_stream()
+        self.i += 1
+        with torch.cuda.stream(self.s_in):
+            if self.consumed[j] is not None:
+                self.s_in.wait_event(self.consumed[j])
+            for d, h in zip(self.dev_inputs[j], self.host_inputs):
+                d.copy_(h, non_blocking=True)
+            arrived = torch.cuda.Event()
+            arrived.record(self.s_in)
+        main.wait_event(arrived)
+        out = self.forward(*self.dev_inputs[j])
+        done = torch.cuda.Event()
+        done.record(main)
+        self.consumed[j] = done
+        out.record_stream(self.s_out)
+        with torch.cuda.stream(self.s_out):
+            self.s_out.wait_event(done)
+            self.out_host[j].copy_(out, non_blocking=True)
+            ev = torch.cuda.Event()
+            ev.record(self.s_out)
+        self.copied_out[j] = ev
+
+    def finish(self):
+        main = torch.cuda.current_stream()
+        for ev in self.copied_out:
+            if ev is not None:
+                main.wait_event(ev)
+
+
 class ClockSampler:
     """Samples nvidia-smi clocks / throttle reasons every 200 ms while the timed region runs."""
     Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
@@ -192,11 +239,7 @@ def run_ep(args, world, rank, local, dev):
     def step_device():
         return forward(x, weights, indices)
 
-    def step_e2e():
-        xd = x_host.to(dev, non_blocking=True)
-        idd = idx_host.to(dev, non_blocking=True)
-        wd = w_host.to(dev, non_blocking=True)
-        out_host.copy_(forward(xd, wd, idd), non_blocking=True)
+    step_e2e = PipelinedE2E((x_host, w_host, idx_host), forward, (T, D), dev)
 
     def timed(fn, steps, warmup):
         for _ in range(warmup):
@@ -207,6 +250,8 @@ def run_ep(args, world, rank, local, dev):
         e0.record()
         for _ in range(steps):
             fn()
+        if hasattr(fn, "finish"):
+            fn.finish()
         e1.record()
         dist.barrier()
         torch.cuda.synchronize()
@@ -279,8 +324,11 @@ def run_ep(args, world, rank, local, dev):
             "e2e": {"value": flops / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s",
                     "ms_per_step": ms_e2e,
                     "h2d_bytes_per_step": x_host.numel() * 2 + idx_host.numel() * 8 + w_host.numel() * 4,
-                    "d2h_bytes_per_step": out_host.numel() * 2},
-            "gpu_launches": world * 14 * args.steps, "clocks": clocks,
+                    "d2h_bytes_per_step": out_host.numel() * 2,
+                    "pipeline": "double-buffered: copies of steps i+1 / i-1 on side streams"},
+            # per rank and step: layout x3, quantiser, row permute, combine + one GEMM pair for
+            # each half of the own run and for each peer's slice (one slice per peer at this size)
+            "gpu_launches": world * args.steps * (6 + 2 * (2 + (world - 1))), "clocks": clocks,
             "roofline": {"bound": "tensor", "kernel": "whole EP step (GEMMs + all-to-all)",
                          "achieved": tfl / world, "peak": 2.0 * bf16_peak, "unit": "TFLOP/s",
                          "frac": tfl / world / (2.0 * bf16_peak), "traffic": None,
@@ -384,12 +432,9 @@ def run_ours(args):
     def step_device():
         return ops.moe_forward_fp8(g["x"], wq, g["weights"], g["indices"], LIMIT)
 
-    def step_e2e():
-        xd = x_host.to(dev, non_blocking=True)
-        idd = idx_host.to(dev, non_blocking=True)
-        wd = w_host.to(dev, non_blocking=True)
-        out = ops.moe_forward_fp8(xd, wq, wd, idd, LIMIT)
-        out_host.copy_(out, non_blocking=True)
+    step_e2e = PipelinedE2E((x_host, w_host, idx_host),
+                            lambda xd, wd, idd: ops.moe_forward_fp8(xd, wq, wd, idd, LIMIT),
+                            (T, D), dev)
 
     def barrier():
         if world > 1:
@@ -404,6 +449,8 @@ def run_ours(args):
         e0.record()
         for _ in range(steps):
             fn()
+        if hasattr(fn, "finish"):
+            fn.finish()
         e1.record()
         barrier()
         ms = e0.elapsed_time(e1)
@@ -521,7 +568,8 @@ def run_ours(args):
         "config": dict(workload_config(), parallelism=f"replicas x{world}" if world > 1 else "1 GPU"),
         "e2e": {"value": world * flops / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s",
                 "ms_per_step": ms_e2e, "h2d_bytes_per_step": bytes_in,
-                "d2h_bytes_per_step": out_host.numel() * 2},
+                "d2h_bytes_per_step": out_host.numel() * 2,
+                "pipeline": "double-buffered: copies of steps i+1 / i-1 on side streams"},
         "gpu_launches": launches_per_step * args.steps,
         "clocks": clocks,
         "scale_fmt": args.scale_fmt, "other_modes": other_modes,
