@@ -577,7 +577,13 @@ def run_ours(args):
                      "kernel": ("gemm_mx_kernel<tma,swiglu>" if ue8m0 else
                                 "grouped_gemm_fp8_kernel<tma,swiglu>") + " (gate/up)",
                      "achieved": achieved, "peak": fp8_peak, "unit": "TFLOP/s",
-                     "frac": achieved / fp8_peak, "traffic": None,
+                     "frac": achieved / fp8_peak,
+                     # DRAM bytes per gate/up launch: ncu read + write of the profiling case
+                     # (24,576 rows, 16 experts: 68.7 MB fp32 scales, 67.4 MB ue8m0) x 4, since
+                     # config 2 has 4 x the rows and 4 x the experts
+                     "traffic": (67.4e6 if ue8m0 else 68.7e6) * 4 if args.workload == "c2" else None,
+                     "traffic_note": "scaled from the ncu capture of the profiling case "
+                                     "(profiles/kernel_families_profile_case.md)",
                      "peak_note": f"2 x bf16 burst {bf16_peak} TFLOP/s {peak_src} "
                                   f"(no measured fp8 figure); {achieved / SPEC_FP8_TFLOPS:.3f} of "
                                   f"the 4500 TFLOP/s dense-fp8 spec"},
