@@ -453,6 +453,25 @@ class SegContext(PeerBuffers):
                                               ops._stream()), "nv41_peer_copy_2d")
 
 
+def plan_segments(B, me: int, slice_rows: int):
+    """What rank ``me`` works on, from the gathered run boundaries B[g] = [first padded row of
+    owner 0's experts, ..., of owner G-1's, end of the last owner's, P of rank g].  Returns
+    (own, jobs): own = (first row, split point, end) of its run in its own buffers, jobs = list
+    of (peer g, first row s0 in g's buffers, rows n) in processing order (peers me+1, me+2, ...
+    cyclically, each run cut into slices of ``slice_rows`` rows).  Host-only; the same plan is
+    computed inside nv41_ep_owner_forward."""
+    world = len(B)
+    slice_rows = max(128, slice_rows // 128 * 128)
+    jobs = []
+    for i in range(1, world):
+        g = (me + i) % world
+        r0, r1 = B[g][me], B[g][me + 1]
+        for s0 in range(r0, r1, slice_rows):
+            jobs.append((g, s0, min(slice_rows, r1 - s0)))
+    o0, o1 = B[me][me], B[me][me + 1]
+    return (o0, o0 + (o1 - o0) // 256 * 128, o1), jobs
+
+
 def moe_forward_fp8_seg(ctx: SegContext, x: torch.Tensor, wq_local: ops.Fp8ExpertWeights,
                         weights: torch.Tensor, indices: torch.Tensor, n_experts: int,
                         limit: float, shared: torch.Tensor | None = None,
@@ -526,34 +545,28 @@ def moe_forward_fp8_seg(ctx: SegContext, x: torch.Tensor, wq_local: ops.Fp8Exper
     ready = torch.cuda.Event()
     ready.record(main)
     cin.wait_event(ready)
-    slice_rows = max(128, slice_rows // 128 * 128)
+    (r0, mid, r1), planned = plan_segments(B, me, slice_rows)
     jobs = []
     with torch.cuda.stream(cin):
-        for i in range(1, world):
-            g = (me + i) % world
-            r0, r1, Pg = B[g][me], B[g][me + 1], B[g][world + 1]
-            for s0 in range(r0, r1, slice_rows):
-                n = min(slice_rows, r1 - s0)
-                ac = torch.empty((n, D), dtype=torch.uint8, device=dev)
-                asc = torch.empty((nkb, n), dtype=torch.float32, device=dev)
-                w = torch.empty(n, dtype=torch.float32, device=dev)
-                tiles = torch.empty(n // 128, dtype=torch.int32, device=dev)
-                sf = torch.empty(n // 128 * nkb * 512, dtype=torch.uint8, device=dev) if ctx.ue8m0 else None
-                ctx.copy(ac.data_ptr(), n * D, ctx.addr("codes", g) + s0 * D, n * D, n * D)
-                ctx.copy(asc.data_ptr(), n * 4, ctx.addr("scales", g) + s0 * 4, Pg * 4, n * 4, nkb)
-                ctx.copy(w.data_ptr(), n * 4, ctx.addr("weight", g) + s0 * 4, n * 4, n * 4)
-                ctx.copy(tiles.data_ptr(), n // 32, ctx.addr("tiles", g) + s0 // 32, n // 32, n // 32)
-                if sf is not None:
-                    nb = n // 128 * nkb * 512
-                    ctx.copy(sf.data_ptr(), nb, ctx.addr("atoms", g) + s0 // 128 * nkb * 512, nb, nb)
-                ev = torch.cuda.Event()
-                ev.record(cin)
-                jobs.append((g, s0, n, ac, asc, sf, w, tiles, ev))
+        for g, s0, n in planned:
+            Pg = B[g][world + 1]
+            ac = torch.empty((n, D), dtype=torch.uint8, device=dev)
+            asc = torch.empty((nkb, n), dtype=torch.float32, device=dev)
+            w = torch.empty(n, dtype=torch.float32, device=dev)
+            tiles = torch.empty(n // 128, dtype=torch.int32, device=dev)
+            sf = torch.empty(n // 128 * nkb * 512, dtype=torch.uint8, device=dev) if ctx.ue8m0 else None
+            ctx.copy(ac.data_ptr(), n * D, ctx.addr("codes", g) + s0 * D, n * D, n * D)
+            ctx.copy(asc.data_ptr(), n * 4, ctx.addr("scales", g) + s0 * 4, Pg * 4, n * 4, nkb)
+            ctx.copy(w.data_ptr(), n * 4, ctx.addr("weight", g) + s0 * 4, n * 4, n * 4)
+            ctx.copy(tiles.data_ptr(), n // 32, ctx.addr("tiles", g) + s0 // 32, n // 32, n // 32)
+            if sf is not None:
+                nb = n // 128 * nkb * 512
+                ctx.copy(sf.data_ptr(), nb, ctx.addr("atoms", g) + s0 // 128 * nkb * 512, nb, nb)
+            ev = torch.cuda.Event()
+            ev.record(cin)
+            jobs.append((g, s0, n, ac, asc, sf, w, tiles, ev))
     # this rank's own run is used in place, half before and half after the peers' slices: the
     # first half hides the first copy-in, the second the last copy-out
-    r0, r1 = B[me][me], B[me][me + 1]
-    mid = r0 + (r1 - r0) // 256 * 128
-
     def own_run(a, b):
         if b > a:
             experts(codes[a:b], scales[:, a:b],

@@ -30,7 +30,7 @@ def make_case(T, E, k, D, I, seed=0, zipf=True, outliers=True, empty_expert=None
     return {n: t.to(device) for n, t in out.items()}
 
 
-# BASELINE.json configs that are standalone expert-path workloads
+# the two standalone expert-path benchmark configurations (single GPU; expert-parallel)
 C2 = dict(T=16384, E=64, k=6, D=1024, I=1024, seed=1, zipf=True, outliers=True)
 C5 = dict(T=131072, E=256, k=8, D=2048, I=1024, seed=2, zipf=False, outliers=False)
 

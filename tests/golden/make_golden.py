@@ -1,7 +1,8 @@
 """Generates the golden fixtures in this directory by running the reference's own Python code
-(CPU) from a checkout given by $NANOV41_REF (default /root/reference).
+(CPU) from a checkout of QingGo/nanov41 whose path is given in $NANOV41_REF.
 
-    NANOV41_MOE_TILE=128,64,128,4,2 NANOV41_MOE_NOPAD=1 python tests/golden/make_golden.py
+    NANOV41_REF=<checkout> NANOV41_MOE_TILE=128,64,128,4,2 NANOV41_MOE_NOPAD=1 \
+        python tests/golden/make_golden.py
 
 The env knobs make the reference's MoELayout use 128-row tiles and emit row_of_flat /
 flat_of_row.  The fixtures are small .npz files; bf16 tensors are stored as their uint16 bit
@@ -18,7 +19,9 @@ import torch
 
 os.environ.setdefault("NANOV41_MOE_TILE", "128,64,128,4,2")
 os.environ.setdefault("NANOV41_MOE_NOPAD", "1")
-REF = os.environ.get("NANOV41_REF", "/root/reference")
+REF = os.environ.get("NANOV41_REF")
+if not REF:
+    sys.exit("set NANOV41_REF to a checkout of the reference repository")
 sys.path.insert(0, REF)
 HERE = Path(__file__).resolve().parent
 

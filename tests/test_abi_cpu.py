@@ -47,3 +47,23 @@ def test_ops_refuse_cpu_tensors():
         ops.quant_fp8_128x128(torch.zeros(1, 128, 128, dtype=torch.bfloat16))
     with pytest.raises(RuntimeError):
         ops.build_layout(torch.zeros(8, dtype=torch.int64), 4, 2)
+
+
+def test_expert_parallel_entry_points_validate_without_gpu():
+    """Host-side argument checks of the peer-memory entry points (no device work is reached)."""
+    import ctypes as C
+    from nanov41_b200 import _lib
+    lib = _lib.load()
+    assert lib.nv41_peer_alloc(0, None) == _lib.ERR_INVALID
+    assert lib.nv41_peer_export(None, None) == _lib.ERR_INVALID
+    assert lib.nv41_peer_open(None, None) == _lib.ERR_INVALID
+    assert lib.nv41_peer_copy_2d(None, 0, None, 0, 16, 1, None) == _lib.ERR_INVALID
+    assert lib.nv41_set_gemm_cta_limit(-1) == _lib.ERR_INVALID
+    assert lib.nv41_set_gemm_cta_limit(0) == _lib.OK
+    bounds = (C.c_longlong * 3)(0, 128, 128)
+    assert lib.nv41_ep_owner_forward(bounds, 1, 0, 100, None, None, None, None, None, None, None,
+                                     None, None, None, None, None) == _lib.ERR_INVALID
+    assert lib.nv41_ep_pull_fp8_rows(None, None, 9, None, None, None, None, 128, 128, 128, 0, 128,
+                                     None, None, None, 0, None, None) == _lib.ERR_INVALID
+    assert lib.nv41_gather_nvfp4_rows(None, None, None, None, 64, 256, 128, None, None,
+                                      None) == _lib.ERR_INVALID

@@ -66,3 +66,76 @@ def test_shard_expert_weights():
     w1 = torch.arange(8 * 2 * 3).view(8, 2, 3)
     a, b, c = ep.shard_expert_weights(w1, w1, w1, 1, 4)
     assert a.shape[0] == 2 and torch.equal(a, w1[2:4]) and torch.equal(c, w1[2:4])
+
+
+def _seg_worker(rank, world, port, T, E, k, D):
+    """Segment path on CPU: every rank lays its rows out expert-major over all experts (oracle
+    layout), the run boundaries are all-gathered, every owner works through ``plan_segments`` on
+    the peers' buffers (exchanged as objects here, peer-mapped HBM on a GPU box) and writes its
+    results into the home rank's rows; the home rank's own row_of_flat then finds them."""
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from nanov41_b200 import ep
+        gen = torch.Generator().manual_seed(7 + rank)
+        El = E // world
+        x = torch.randn(T, D, generator=gen)
+        idx = torch.stack([torch.randperm(E, generator=gen)[:k] for _ in range(T)])
+        if rank == 1:
+            idx = idx % El                        # rank 1 routes only to rank 0's experts
+        lay = OL.padded_layout(idx.reshape(-1), E, k)
+        P = lay["P_max"]
+        flat_of_row = lay["flat_of_row"]
+        rows = torch.zeros(P, D)
+        real = flat_of_row >= 0
+        rows[real] = x[flat_of_row[real] // k]
+        tiles = torch.where(lay["tile_e"] >= 0, lay["tile_e"] % El, lay["tile_e"])
+        mine = lay["pad_off"][::El].tolist() + [P]
+        B = [None] * world
+        dist.all_gather_object(B, mine)
+        bufs = [None] * world
+        dist.all_gather_object(bufs, dict(rows=rows, tiles=tiles))
+        (o0, omid, o1), jobs = ep.plan_segments(B, rank, slice_rows=256)
+        assert o0 <= omid <= o1 and omid % 128 == 0
+        work = [(rank, o0, omid - o0), (rank, omid, o1 - omid)] + jobs
+        results = []                              # (home rank, first row, y rows)
+        for g, s0, n in work:
+            if n == 0:
+                continue
+            assert s0 % 128 == 0 and n % 128 == 0 and B[g][rank] <= s0 and s0 + n <= B[g][rank + 1]
+            t = bufs[g]["tiles"][s0 // 128:(s0 + n) // 128]
+            assert torch.all((t >= 0) & (t < El))          # only experts this rank owns
+            e_global = (t + rank * El).repeat_interleave(128).float()
+            results.append((g, s0, bufs[g]["rows"][s0:s0 + n] * (e_global + 1.0)[:, None]))
+        everyone = [None] * world
+        dist.all_gather_object(everyone, results)
+        y = torch.full((P, D), float("nan"))
+        covered = torch.zeros(P, dtype=torch.int64)
+        for owner_results in everyone:
+            for g, s0, yr in owner_results:
+                if g == rank:
+                    y[s0:s0 + yr.shape[0]] = yr
+                    covered[s0:s0 + yr.shape[0]] += 1
+        used = int(lay["pad_off"][-1])
+        assert torch.all(covered[:used] == 1) and torch.all(covered[used:] == 0)
+        out = y[lay["row_of_flat"]].view(T, k, D).sum(1)
+        want = (x[:, None, :] * (idx.float() + 1.0)[:, :, None]).sum(1)
+        assert torch.allclose(out, want, rtol=1e-6, atol=1e-6)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_segment_plan_two_ranks():
+    mp.spawn(_seg_worker, args=(2, _free_port(), 300, 8, 3, 16), nprocs=2, join=True)
+
+
+def test_plan_segments_slices_and_order():
+    from nanov41_b200 import ep
+    # 3 ranks; B[g] = [run starts of owners 0..2, end, P]
+    B = [[0, 256, 256, 640, 1024], [0, 128, 512, 512, 768], [0, 0, 384, 896, 1024]]
+    own, jobs = ep.plan_segments(B, 1, slice_rows=128)
+    assert own == (128, 256, 512)
+    assert jobs == [(2, 0, 128), (2, 128, 128), (2, 256, 128)]     # rank 0 has no rows for owner 1
+    own, jobs = ep.plan_segments(B, 2, slice_rows=256)
+    assert own == (384, 640, 896)
+    assert jobs == [(0, 256, 256), (0, 512, 128)]                   # rank 1 has none for owner 2
