@@ -432,9 +432,11 @@ class SegContext(PeerBuffers):
     experts (each expert's run padded to 128 rows) in peer-mapped buffers: FP8 codes [P, D], K-major
     scales [D/128, P], router weight per row [P], local expert id per 128-row tile [P/128] (and
     the e8m0 scale atoms for ue8m0 weights), plus ``y`` bf16 [P, D] for the results.  The rows of
-    the experts a rank owns are then one contiguous run of tiles in every rank's buffers."""
+    the experts a rank owns are then one contiguous run of tiles in every rank's buffers.
+    ``backward=True`` adds the buffers of the training path (``ep_autograd``)."""
 
-    def __init__(self, t_max: int, k: int, n_experts: int, D: int, ue8m0: bool = False, group=None):
+    def __init__(self, t_max: int, k: int, n_experts: int, D: int, ue8m0: bool = False, group=None,
+                 backward: bool = False):
         if D % 128:
             raise ops.Nv41Error("expert parallelism needs D % 128 == 0")
         P = ops.p_max_for(t_max * k, n_experts)
@@ -443,6 +445,8 @@ class SegContext(PeerBuffers):
                  "y": P * D * 2}
         if ue8m0:
             sizes["atoms"] = P // 128 * nkb * 512
+        if backward:      # training (ep_autograd): bf16 dOut / x rows out, dX rows and dws back
+            sizes.update({"dy16": P * D * 2, "x16": P * D * 2, "dx": P * D * 2, "dws": P * 4})
         super().__init__(sizes, group)
         self.t_max, self.k, self.E, self.D, self.P, self.ue8m0 = t_max, k, n_experts, D, P, ue8m0
         self.dummy = torch.zeros(1, dtype=torch.int32, device=self.dev)

@@ -1,0 +1,198 @@
+"""Forward + backward of the routed experts under expert parallelism (segment path).
+
+Same data flow as the single-GPU ``autograd_moe._RoutedExperts`` (the structure of
+nanov41/triton_grouped_moe.py:1461-1483, _GroupedMoEv2FP8.backward), with the rows of every
+expert processed on the rank that owns it:
+
+forward   home: layout over all experts, x quantised once per token and permuted into the
+          peer-mapped buffers.  owner: for its run of every rank's buffers (its own in place,
+          a peer's copied in with the copy engines): gate/up GEMM (+SwiGLU, re-quantised h,
+          gate / up / h kept in bf16 for the backward), down GEMM, results copied into the home
+          rank's ``y``.  home: fp32 top-k sum.
+backward  home: dOut quantised once per token and permuted (FP8 codes + scales for the dact
+          GEMM), bf16 copies of the permuted dOut and x rows for the weight gradients.
+          owner, per run: dact = dY @ W2 (FP8), SwiGLU backward + dws, dX rows = [dgate|dup] @
+          [W1;W3] (FP8) copied into the home rank's ``dx`` rows, dws into its ``dws`` rows, and
+          dW2 / dW1 / dW3 of the LOCAL experts accumulated over the runs in fp32.
+          home: fp32 slot sum of the dX rows, dws read back per (token, slot).
+
+Ordering between ranks: one all-gather of the padded segment offsets (host-read) in the forward,
+one-word all-reduces as fences before the owners read and after they have written.  fp32 block
+scales only.  Everything is issued on the current stream.
+"""
+from __future__ import annotations
+
+from dataclasses import replace
+
+import torch
+import torch.distributed as dist
+
+from . import ops
+from .ep import SegContext
+
+
+def _runs(everyone, me: int, world: int, El: int):
+    """(rank g, first row, end row, P of g, pad_off of my experts in g's buffers) for g = me,
+    me+1, ... cyclically."""
+    out = []
+    for i in range(world):
+        g = (me + i) % world
+        po = everyone[g][me * El:(me + 1) * El + 1]
+        out.append((g, po[0], po[-1], everyone[g][-1], po))
+    return out
+
+
+class _RoutedExpertsSeg(torch.autograd.Function):
+    @staticmethod
+    def forward(actx, x, ws, shared, w1, w3, w2, indices, limit, wq, seg: SegContext, n_experts):
+        if wq.ue8m0:
+            raise ops.Nv41Error("expert-parallel training path: fp32 block scales only")
+        world, me, dev = seg.world, seg.rank, seg.dev
+        T, D = x.shape
+        k = indices.shape[1]
+        El = n_experts // world
+        nkb = D // 128
+        need_grad = any(actx.needs_input_grad)
+        if T > seg.t_max or k != seg.k or D != seg.D or n_experts != seg.E or wq.E != El:
+            raise ops.Nv41Error("SegContext / weights were sized for another problem")
+        x = x.contiguous()
+        lay = ops.build_layout(indices.reshape(-1), n_experts, k, ws.reshape(-1))
+        P = lay.P_max
+        own = seg.own
+        codes = own["codes"][:P * D].view(P, D)
+        scales = own["scales"].view(torch.float32)[:nkb * P].view(nkb, P)
+        y_mine = own["y"].view(torch.bfloat16)[:P * D].view(P, D)
+        xc, xs = ops.quant_fp8_1x128(x, scale_kmajor=True)
+        ops.gather_fp8_rows(xc, xs, lay, False, out=(codes, scales, None))
+        w_rows = own["weight"].view(torch.float32)[:P]
+        w_rows.copy_(lay.row_weight)
+        t_rows = own["tiles"].view(torch.int32)[:P // 128]
+        te = lay.tile_expert
+        t_rows.copy_(torch.where(te >= 0, te % El, te))
+        mine = torch.cat((lay.pad_off, torch.tensor([P], dtype=torch.int32, device=dev)))
+        gathered = torch.empty((world, n_experts + 2), dtype=torch.int32, device=dev)
+        dist.all_gather_into_tensor(gathered, mine.contiguous(), group=seg.group)
+        everyone = gathered.tolist()                 # the one host synchronisation
+        runs = _runs(everyone, me, world, El)
+        saved = []
+        for g, r0, r1, Pg, po in runs:
+            n = r1 - r0
+            if n == 0:
+                saved.append(None)
+                continue
+            if g == me:
+                ac, asc, w, tiles = codes[r0:r1], scales[:, r0:r1], w_rows[r0:r1], t_rows[r0 // 128:r1 // 128]
+                y = y_mine[r0:r1]
+            else:
+                ac = torch.empty((n, D), dtype=torch.uint8, device=dev)
+                asc = torch.empty((nkb, n), dtype=torch.float32, device=dev)
+                w = torch.empty(n, dtype=torch.float32, device=dev)
+                tiles = torch.empty(n // 128, dtype=torch.int32, device=dev)
+                seg.copy(ac.data_ptr(), n * D, seg.addr("codes", g) + r0 * D, n * D, n * D)
+                seg.copy(asc.data_ptr(), n * 4, seg.addr("scales", g) + r0 * 4, Pg * 4, n * 4, nkb)
+                seg.copy(w.data_ptr(), n * 4, seg.addr("weight", g) + r0 * 4, n * 4, n * 4)
+                seg.copy(tiles.data_ptr(), n // 32, seg.addr("tiles", g) + r0 // 32, n // 32, n // 32)
+                y = None
+            if need_grad and g == me:     # the buffers are rewritten before the backward runs
+                w, tiles = w.clone(), tiles.clone()
+            pad_off = torch.tensor([v - r0 for v in po], dtype=torch.int32, device=dev)
+            meta = torch.tensor([n // 128, n, n, El], dtype=torch.int32, device=dev)
+            sub = replace(lay, E=El, P_max=n, tile_expert=tiles, row_weight=w, row_token=seg.dummy,
+                          flat_of_row=seg.dummy, pad_off=pad_off, meta=meta)
+            h_codes, h_scale, gate, up, h = ops.gemm1_fp8(ops.A_CONTIGUOUS, ac, asc, wq.w13_codes,
+                                                          wq.w13_scale, sub, limit,
+                                                          save_gate_up=need_grad, save_h=need_grad)
+            y = ops.gemm_fp8(ops.A_CONTIGUOUS, h_codes, h_scale, wq.w2_codes, wq.w2_scale, sub, out=y)
+            if g != me:
+                seg.copy(seg.addr("y", g) + r0 * D * 2, n * D * 2, y.data_ptr(), n * D * 2, n * D * 2)
+            saved.append((sub, gate, up, h, y))      # y kept alive until the fence below
+        seg.fence()
+        out = ops.combine(y_mine, lay.row_of_flat, T, k, shared)
+        if need_grad:
+            actx.save_for_backward(x)
+            actx.state = (seg, wq, lay, runs, [None if s is None else s[:4] for s in saved], limit,
+                          n_experts, shared is not None, (w1.shape, w3.shape, w2.shape))
+        return out
+
+    @staticmethod
+    def backward(actx, dout):
+        (x,) = actx.saved_tensors
+        seg, wq, lay, runs, saved, limit, n_experts, has_shared, wshapes = actx.state
+        if wq.w2_codes_t is None:
+            raise ops.Nv41Error("backward needs the transposed weight codes "
+                                "(quantize_expert_weights(..., transposed=True))")
+        if "dx" not in seg.own:
+            raise ops.Nv41Error("SegContext(..., backward=True) is needed for training")
+        world, me, dev = seg.world, seg.rank, seg.dev
+        T, D = x.shape
+        k, P, I = lay.k, lay.P_max, wq.I
+        nkb = D // 128
+        own = seg.own
+        bf = lambda name: own[name].view(torch.bfloat16)[:P * D].view(P, D)
+        dout = dout.to(torch.bfloat16).contiguous()
+        codes = own["codes"][:P * D].view(P, D)
+        scales = own["scales"].view(torch.float32)[:nkb * P].view(nkb, P)
+        dqc, dqs = ops.quant_fp8_1x128(dout, scale_kmajor=True)
+        ops.gather_fp8_rows(dqc, dqs, lay, False, out=(codes, scales, None))
+        need_w = any(actx.needs_input_grad[3:6])
+        dy16, x16 = bf("dy16"), bf("x16")
+        if need_w:
+            ops.gather_rows(dout, lay.row_token, out=dy16)
+            ops.gather_rows(x, lay.row_token, out=x16)
+        seg.fence()                                   # every rank's buffers hold this step's rows
+        dw = [torch.zeros(s, dtype=torch.float32, device=dev) for s in wshapes] if need_w else None
+        keep = []
+        for (g, r0, r1, Pg, _), sv in zip(runs, saved):
+            n = r1 - r0
+            if n == 0:
+                continue
+            sub, gate, up, h = sv
+            if g == me:
+                dyc, dys = codes[r0:r1], scales[:, r0:r1]
+                dy_rows, x_rows = dy16[r0:r1], x16[r0:r1]
+            else:
+                dyc = torch.empty((n, D), dtype=torch.uint8, device=dev)
+                dys = torch.empty((nkb, n), dtype=torch.float32, device=dev)
+                seg.copy(dyc.data_ptr(), n * D, seg.addr("codes", g) + r0 * D, n * D, n * D)
+                seg.copy(dys.data_ptr(), n * 4, seg.addr("scales", g) + r0 * 4, Pg * 4, n * 4, nkb)
+                if need_w:
+                    dy_rows = torch.empty((n, D), dtype=torch.bfloat16, device=dev)
+                    x_rows = torch.empty((n, D), dtype=torch.bfloat16, device=dev)
+                    seg.copy(dy_rows.data_ptr(), n * D * 2, seg.addr("dy16", g) + r0 * D * 2, n * D * 2, n * D * 2)
+                    seg.copy(x_rows.data_ptr(), n * D * 2, seg.addr("x16", g) + r0 * D * 2, n * D * 2, n * D * 2)
+            dact = ops.gemm_fp8(ops.A_CONTIGUOUS, dyc, dys, wq.w2_codes_t, wq.w2_scale, sub,
+                                b_scale_transposed=True)[:, :I]
+            if not dact.is_contiguous():
+                dact = dact.contiguous()
+            dgate, dup, dgu_codes, dgu_scale, dws_rows = ops.swiglu_bwd_quant(dact, gate, up, sub, limit)
+            dx_rows = ops.gemm_fp8(ops.A_CONTIGUOUS, dgu_codes, dgu_scale, wq.w13_codes_t,
+                                   wq.w13_scale, sub, b_scale_transposed=True)
+            if dx_rows.shape[1] != D:
+                dx_rows = dx_rows[:, :D].contiguous()
+            seg.copy(seg.addr("dx", g) + r0 * D * 2, n * D * 2, dx_rows.data_ptr(), n * D * 2, n * D * 2)
+            seg.copy(seg.addr("dws", g) + r0 * 4, n * 4, dws_rows.data_ptr(), n * 4, n * 4)
+            keep.append((dx_rows, dws_rows))
+            if need_w:
+                dw[2] += ops.wgrad_bf16(dy_rows.contiguous(), h, sub)          # [El, D, I]
+                dw[0] += ops.wgrad_bf16(dgate, x_rows.contiguous(), sub)       # [El, I, D]
+                dw[1] += ops.wgrad_bf16(dup, x_rows.contiguous(), sub)
+        seg.fence()                                   # dx / dws rows of every owner have landed
+        dx = ops.combine(bf("dx"), lay.row_of_flat, T, k)
+        dws = own["dws"].view(torch.float32)[:P][lay.row_of_flat.long()].view(T, k)
+        dshared = dout if has_shared else None
+        dw1 = dw3 = dw2 = None
+        if need_w:
+            dw1, dw3, dw2 = (t.to(torch.bfloat16) for t in dw)
+        return dx, dws, dshared, dw1, dw3, dw2, None, None, None, None, None
+
+
+def experts_forward_ep(seg: SegContext, x, ws, indices, w1_local, w3_local, w2_local, n_experts: int,
+                       limit: float, shared=None, wq_local=None):
+    """Differentiable expert-parallel routed experts.  x [T_local, D] bf16; ws / indices
+    [T_local, k] (global expert ids); w*_local: this rank's experts ([E/G, I, D], [E/G, I, D],
+    [E/G, D, I] bf16).  Gradients: x, ws, shared, and the local weights (summed over the rows of
+    all ranks).  ``wq_local``: pre-quantised local weights with transposed copies (optional)."""
+    if wq_local is None:
+        wq_local = ops.quantize_expert_weights(w1_local, w3_local, w2_local, transposed=True)
+    return _RoutedExpertsSeg.apply(x, ws, shared, w1_local, w3_local, w2_local, indices,
+                                   float(limit or 0.0), wq_local, seg, n_experts)

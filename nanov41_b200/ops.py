@@ -382,12 +382,16 @@ def quantize_expert_weights(w1: torch.Tensor, w3: torch.Tensor, w2: torch.Tensor
     return wq
 
 
-def gather_rows(src: torch.Tensor, rows: torch.Tensor) -> torch.Tensor:
-    """dst[p] = src[rows[p]] (zero row where rows[p] < 0); bf16 [n, cols] -> [len(rows), cols]."""
+def gather_rows(src: torch.Tensor, rows: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """dst[p] = src[rows[p]] (zero row where rows[p] < 0); bf16 [n, cols] -> [len(rows), cols]
+    (into ``out``, contiguous and of that shape, when given)."""
     _need_cuda(src, rows)
     if src.dtype != torch.bfloat16 or src.dim() != 2 or src.stride(1) != 1:
         raise Nv41Error("gather_rows expects a 2-D bf16 tensor with unit inner stride")
-    out = torch.empty((rows.numel(), src.shape[1]), dtype=torch.bfloat16, device=src.device)
+    if out is None:
+        out = torch.empty((rows.numel(), src.shape[1]), dtype=torch.bfloat16, device=src.device)
+    elif out.shape != (rows.numel(), src.shape[1]) or not out.is_contiguous():
+        raise Nv41Error("gather_rows: out has the wrong shape")
     check(_lib.load().nv41_gather_rows_bf16(_ptr(src), src.stride(0), _ptr(rows), rows.numel(),
                                             src.shape[1], _ptr(out), _stream()),
           "nv41_gather_rows_bf16")
