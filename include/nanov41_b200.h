@@ -219,12 +219,14 @@ int nv41_moe_gemm_nvfp4(const void* a_packed, const void* a_sf, float a_global,
  * in 16-element blocks -> h_packed [P_max, h_kpad/2] + scale atoms [P_max/128][h_kpad/64][512]
  * (columns [I, h_kpad) are left untouched: zero them once).  Bit-identical to
  * nv41_moe_gemm_nvfp4 -> nv41_swiglu_quant_nvfp4 without the bf16 gate|up round trip through
- * HBM.  w13 rows per expert are INTERLEAVED in groups of 64: [W1[0:64]; W3[0:64]; W1[64:128];
- * W3[64:128]; ...] (so one 128-row tile of B holds gate | up of 64 columns); I % 64 == 0,
- * Kpad % 256 == 0, h_kpad % 256 == 0. */
+ * HBM.  w13 rows per expert are INTERLEAVED in groups of `interleave` = 64 or 128 rows:
+ * [W1[0:g]; W3[0:g]; W1[g:2g]; W3[g:2g]; ...], so one tile of 2g rows of B holds gate | up of g
+ * columns of h (g = 128 selects the 128 x 256 tile); I % interleave == 0, Kpad % 256 == 0,
+ * h_kpad % 256 == 0. */
 int nv41_moe_gemm1_nvfp4(const void* a_packed, const void* a_sf, float a_global,
                          const void* w13_packed, const void* w13_sf, const float* w13_global,
-                         int E, int I, int Kpad, const int* tile_expert, const float* row_weight,
+                         int E, int I, int interleave, int Kpad, const int* tile_expert,
+                         const float* row_weight,
                          long long P_max, float swiglu_limit, float h_global, void* h_packed,
                          void* h_sf, int h_kpad, unsigned* status, void* stream);
 

@@ -109,14 +109,6 @@ gather_nvfp4_rows_kernel(const uint8_t* __restrict__ packed, const uint8_t* __re
   }
 }
 
-__device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
-  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    f[2 * i] = __uint_as_float(w[i] << 16);
-    f[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
-  }
-}
 __device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
   uint32_t o[4];
 #pragma unroll
@@ -132,17 +124,6 @@ __device__ __forceinline__ uint2 quant8(const float (&f)[8], float s) {
                     e4m3x4_div(f[4], f[5], f[6], f[7], s, r));
 }
 
-// fp32 block scale, or (ue8m0) rounded up to a power of two: ref/kernel.py:22-37,76-80
-__device__ __forceinline__ float block_scale(float amax, int ue8m0) {
-  float s = fmaxf(amax, 1e-4f) * (1.0f / 448.0f);
-  if (ue8m0) {
-    const uint32_t b = __float_as_uint(s);
-    uint32_t e = (b >> 23) & 0xFFu;
-    if (b & 0x7FFFFFu) ++e;
-    s = __uint_as_float(e << 23);
-  }
-  return s;
-}
 
 // One warp per padded row; a half-warp (16 lanes x 8 columns) covers one 1x128 block.
 __global__ void __launch_bounds__(256)
@@ -168,9 +149,9 @@ swiglu_bwd_quant_kernel(const __nv_bfloat16* __restrict__ dact, const __nv_bfloa
 #pragma unroll
       for (int i = 0; i < 8; ++i) d[i] = g[i] = u[i] = 0.f;
       if (in) {
-        unpack8(__ldg(reinterpret_cast<const uint4*>(dact + p * I + col)), d);
-        unpack8(__ldg(reinterpret_cast<const uint4*>(gate + p * I + col)), g);
-        unpack8(__ldg(reinterpret_cast<const uint4*>(up + p * I + col)), u);
+        unpack_bf16x8(__ldg(reinterpret_cast<const uint4*>(dact + p * I + col)), d);
+        unpack_bf16x8(__ldg(reinterpret_cast<const uint4*>(gate + p * I + col)), g);
+        unpack_bf16x8(__ldg(reinterpret_cast<const uint4*>(up + p * I + col)), u);
       }
       float am_g = 0.f, am_u = 0.f;
 #pragma unroll

@@ -32,6 +32,7 @@
 
 #include "../../include/nanov41_b200.h"
 #include "ptx.cuh"
+#include "quant_math.cuh"
 #include "tmap.cuh"
 #include "util.cuh"
 
@@ -114,24 +115,6 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float a, float b) {
 }
 __device__ __forceinline__ float bf16_lo(uint32_t w) { return __uint_as_float(w << 16); }
 __device__ __forceinline__ float bf16_hi(uint32_t w) { return __uint_as_float(w & 0xFFFF0000u); }
-
-// Correctly rounded a / s from r = RN(1 / s): two FMA correction steps (no special cases are
-// needed for the operand range of the quantizer: s >= 1e-4/448, |a / s| <= 448 (1 + eps)).
-__device__ __forceinline__ float div_by_scale(float a, float s, float r) {
-  float q = a * r;
-  float e = fmaf(-s, q, a);
-  q = fmaf(e, r, q);
-  e = fmaf(-s, q, a);
-  return copysignf(fmaf(e, r, q), a);   // keeps -0.0 (code 0x80), which the FMA chain loses
-}
-// e4m3 codes (round-to-nearest-even, saturating at +-448) of four quotients
-__device__ __forceinline__ uint32_t e4m3x4(float a, float b, float c, float d, float s, float r) {
-  const uint32_t lo = __nv_cvt_float2_to_fp8x2(
-      make_float2(div_by_scale(a, s, r), div_by_scale(b, s, r)), __NV_SATFINITE, __NV_E4M3);
-  const uint32_t hi = __nv_cvt_float2_to_fp8x2(
-      make_float2(div_by_scale(c, s, r), div_by_scale(d, s, r)), __NV_SATFINITE, __NV_E4M3);
-  return lo | (hi << 16);
-}
 
 #define NV41_FOR_EACH_UNIT(g, mt, nt, e)                                   \
   for (int w_ = blockIdx.x, total_ = (g).n_tiles_m * (g).n_tiles_n, mt = 0, nt = 0, e = 0; \
@@ -446,15 +429,16 @@ __device__ __forceinline__ void role_swiglu(const GemmArgs& g, const SM& sm, int
     const float s = fmaxf(amax, 1e-4f) * (1.0f / 448.0f);
     const float r = __frcp_rn(s);
     uint8_t* hc = g.h_codes + grow * g.h_ld + ocol;
+    // h values are finite bf16 numbers (amax below is finite, or the row is garbage anyway):
+    // packed two-lane division, correctly rounded, -0.0 keeps its sign (quant_math.cuh)
+    const uint64_t ns2 = f32x2_pack(-s, -s), r2 = f32x2_pack(r, r);
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-      uint32_t wds[4];
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const uint32_t p0 = hp[i * 8 + j * 2], p1 = hp[i * 8 + j * 2 + 1];
-        wds[j] = e4m3x4(bf16_lo(p0), bf16_hi(p0), bf16_lo(p1), bf16_hi(p1), s, r);
-      }
-      *reinterpret_cast<uint4*>(hc + i * 16) = make_uint4(wds[0], wds[1], wds[2], wds[3]);
+      const uint2 lo = e4m3x8_div_bf16(
+          make_uint4(hp[i * 8], hp[i * 8 + 1], hp[i * 8 + 2], hp[i * 8 + 3]), ns2, r2);
+      const uint2 hi = e4m3x8_div_bf16(
+          make_uint4(hp[i * 8 + 4], hp[i * 8 + 5], hp[i * 8 + 6], hp[i * 8 + 7]), ns2, r2);
+      *reinterpret_cast<uint4*>(hc + i * 16) = make_uint4(lo.x, lo.y, hi.x, hi.y);
     }
     g.h_scale[nt * g.h_scale_nb_stride + grow] = s;
     ++unit;

@@ -16,11 +16,16 @@
 // (the order of CUTLASS's Sm1xxBlockScaledBasicChunk K-major atom).  One tcgen05.cp
 // (32x128b.warpx4) moves one atom = the scales of 128 rows x 64 k into 4 TMEM columns.
 //
-// CTA (384 threads): warp 0 TMA producer (A/B tiles + the stage's scale atoms by bulk copy),
-// warp 1 issues scale copies and UMMAs (+ owns TMEM), warps 4-11 epilogue.  Tile 128 x 128,
-// stage = 256 k (128 bytes per row = one swizzle row, four UMMAs of K = 64).  TMEM: two
-// 128-column accumulators (the store of one tile overlaps the next mainloop) + 32 columns of
-// scales.  All mbarrier waits are bounded.
+// CTA: warp 0 TMA producer (A/B tiles + the stage's scale atoms by bulk copy), warp 1 issues
+// scale copies and UMMAs (+ owns TMEM), warps 4.. epilogue (8 warps for the plain store, 16 for
+// the fused SwiGLU + NVFP4 re-quantisation).  Stage = 256 k (128 bytes per row = one swizzle row,
+// four UMMAs of K = 64).  Two tile widths, chosen by the launcher:
+//   N = 128: 36 KiB stages x 5, two 128-column TMEM accumulators (the epilogue of one tile
+//            overlaps the next mainloop);
+//   N = 256: 54 KiB stages x 4 (a third less operand traffic per FLOP), one 256-column
+//            accumulator that the epilogue copies to registers and releases at once.
+// Scale factors live in TMEM columns 256.. (16 for A, 16 or 32 for B).  All mbarrier waits are
+// bounded.
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cstdint>
@@ -35,16 +40,23 @@
 namespace nv41 {
 namespace fp4 {
 
-constexpr int kTM = 128, kTN = 128;
+constexpr int kTM = 128;
 constexpr int kStageK = 256;                      // fp4 elements per stage = 128 bytes per row
-constexpr int kABytes = kTM * 128, kBBytes = kTN * 128;
-constexpr int kSfBytes = 4 * 512;                 // 4 k-groups x one 128-row atom
-constexpr int kStageBytes = kABytes + kBBytes + 2 * kSfBytes;   // 36 KiB
-constexpr int kStages = 5;
+constexpr int kABytes = kTM * 128;
+constexpr int kSfAtomBytes = 4 * 512;             // 4 k-groups x one 128-row atom
 constexpr int kThreads = 384;            // plain store epilogue: 4 + 8 warps
 constexpr int kThreadsFused = 640;       // SwiGLU + NVFP4 epilogue: 4 + 16 warps
-constexpr int kSmemBytes = kStages * kStageBytes + (2 * kStages + 4) * 8 + 16 + 1024;
 constexpr uint32_t kColSfa = 256, kColSfb = 272;  // TMEM columns of the scale factors
+
+template <int TN>
+struct Cfg {
+  static constexpr int kBBytes = TN * 128;
+  static constexpr int kSfbBytes = (TN / 128) * kSfAtomBytes;
+  static constexpr int kStageBytes = kABytes + kBBytes + kSfAtomBytes + kSfbBytes;
+  static constexpr int kStages = TN == 128 ? 5 : 4;
+  static constexpr int kAccBufs = TN == 128 ? 2 : 1;
+  static constexpr int kSmemBytes = kStages * kStageBytes + (2 * kStages + 4) * 8 + 16 + 1024;
+};
 
 struct Args {
   CUtensorMap tmap_a;            // packed A [P_max, Kpad/2] bytes, box 128 x 128
@@ -69,18 +81,20 @@ struct Args {
 
 constexpr int EPI_STORE = 0, EPI_SWIGLU_FP4 = 1;
 
+template <int TN>
 struct Smem {
+  using C = Cfg<TN>;
   uint8_t* base;
-  __device__ uint8_t* a(int s) const { return base + s * kStageBytes; }
-  __device__ uint8_t* b(int s) const { return base + s * kStageBytes + kABytes; }
-  __device__ uint8_t* sfa(int s) const { return base + s * kStageBytes + kABytes + kBBytes; }
-  __device__ uint8_t* sfb(int s) const { return sfa(s) + kSfBytes; }
-  __device__ uint64_t* bars() const { return reinterpret_cast<uint64_t*>(base + kStages * kStageBytes); }
+  __device__ uint8_t* a(int s) const { return base + s * C::kStageBytes; }
+  __device__ uint8_t* b(int s) const { return a(s) + kABytes; }
+  __device__ uint8_t* sfa(int s) const { return b(s) + C::kBBytes; }
+  __device__ uint8_t* sfb(int s) const { return sfa(s) + kSfAtomBytes; }   // [atom of N][k-group][512]
+  __device__ uint64_t* bars() const { return reinterpret_cast<uint64_t*>(base + C::kStages * C::kStageBytes); }
   __device__ uint64_t* full(int s) const { return bars() + s; }
-  __device__ uint64_t* empty(int s) const { return bars() + kStages + s; }
-  __device__ uint64_t* tfull(int b) const { return bars() + 2 * kStages + b; }
-  __device__ uint64_t* tempty(int b) const { return bars() + 2 * kStages + 2 + b; }
-  __device__ uint32_t* tmem_slot() const { return reinterpret_cast<uint32_t*>(bars() + 2 * kStages + 4); }
+  __device__ uint64_t* empty(int s) const { return bars() + C::kStages + s; }
+  __device__ uint64_t* tfull(int b) const { return bars() + 2 * C::kStages + b; }
+  __device__ uint64_t* tempty(int b) const { return bars() + 2 * C::kStages + 2 + b; }
+  __device__ uint32_t* tmem_slot() const { return reinterpret_cast<uint32_t*>(bars() + 2 * C::kStages + 4); }
   __device__ volatile uint32_t* abort_flag() const { return tmem_slot() + 1; }
 };
 
@@ -127,11 +141,13 @@ __device__ __forceinline__ void umma_nvfp4(uint32_t tmem_d, uint64_t adesc, uint
        w_ < total_; w_ += gridDim.x)                                                              \
     if ((mt = w_ / (g).n_tiles_n, nt = w_ - mt * (g).n_tiles_n, e = (g).tile_expert[mt]) >= 0)
 
-template <int EPI>
+template <int EPI, int TN>
 __global__ void __launch_bounds__(EPI == EPI_SWIGLU_FP4 ? kThreadsFused : kThreads, 1)
 nvfp4_gemm_kernel(const __grid_constant__ Args g) {
+  using C = Cfg<TN>;
+  constexpr int kStages = C::kStages, kAccBufs = C::kAccBufs, kNAtoms = TN / 128;
   extern __shared__ uint8_t smem_raw[];
-  Smem sm;
+  Smem<TN> sm;
   sm.base = reinterpret_cast<uint8_t*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -163,7 +179,7 @@ nvfp4_gemm_kernel(const __grid_constant__ Args g) {
     uint32_t it = 0;
     bool ok = true;
     NV41_FP4_FOR_EACH_UNIT(g, mt, nt, e) {
-      const int brow = e * g.N + nt * kTN;
+      const int brow = e * g.N + nt * TN;
       const uint8_t* sfa = g.sfa + static_cast<long long>(mt) * g.kgroups * 512;
       const uint8_t* sfb = g.sfb + static_cast<long long>(brow / 128) * g.kgroups * 512;
       for (int ks = 0; ks < g.nstage && ok; ++ks, ++it) {
@@ -171,21 +187,26 @@ nvfp4_gemm_kernel(const __grid_constant__ Args g) {
         const uint32_t ph = (it / kStages) & 1u;
         ok = mbar_wait(sm.empty(s), ph ^ 1u, sm.abort_flag(), g.status, ST_TIMEOUT_EMPTY);
         if (!ok) break;
-        mbar_arrive_expect_tx(sm.full(s), kStageBytes);
+        mbar_arrive_expect_tx(sm.full(s), C::kStageBytes);
         tma_load_2d(sm.a(s), &g.tmap_a, ks * 128, mt * kTM, sm.full(s));
-        tma_load_2d(sm.b(s), &g.tmap_b, ks * 128, brow, sm.full(s));
-        bulk_load(sm.sfa(s), sfa + ks * kSfBytes, kSfBytes, sm.full(s));
-        bulk_load(sm.sfb(s), sfb + ks * kSfBytes, kSfBytes, sm.full(s));
+        bulk_load(sm.sfa(s), sfa + ks * kSfAtomBytes, kSfAtomBytes, sm.full(s));
+#pragma unroll
+        for (int a = 0; a < kNAtoms; ++a) {      // 128 rows of B and their scale atoms at a time
+          tma_load_2d(sm.b(s) + a * 128 * 128, &g.tmap_b, ks * 128, brow + a * 128, sm.full(s));
+          bulk_load(sm.sfb(s) + a * kSfAtomBytes,
+                    sfb + static_cast<long long>(a) * g.kgroups * 512 + ks * kSfAtomBytes,
+                    kSfAtomBytes, sm.full(s));
+        }
       }
       if (!ok) break;
     }
   } else if (warp == 1 && lane == 0) {
     // ---------------------------------------------------------------- scale copies + UMMAs
-    constexpr uint32_t idesc = idesc_nvfp4(kTM, kTN);
+    constexpr uint32_t idesc = idesc_nvfp4(kTM, TN);
     uint32_t it = 0, nunit = 0;
     bool ok = true;
     NV41_FP4_FOR_EACH_UNIT(g, mt, nt, e) {
-      const uint32_t b = nunit & 1u, tph = (nunit >> 1) & 1u;
+      const uint32_t b = nunit % kAccBufs, tph = (nunit / kAccBufs) & 1u;
       if (!mbar_wait(sm.tempty(b), tph ^ 1u, sm.abort_flag(), g.status, ST_TIMEOUT_TMEM_EMPTY)) break;
       tc_fence_after_sync();
       for (int ks = 0; ks < g.nstage; ++ks, ++it) {
@@ -198,14 +219,18 @@ nvfp4_gemm_kernel(const __grid_constant__ Args g) {
         const uint64_t bdesc = umma_desc_kmajor_sw128(smem_u32(sm.b(s)));
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-          // scales of k-group j of this stage: one atom for A, one for B -> 4 TMEM columns each
+          // scales of k-group j of this stage: one atom for A, one per 128 rows of B -> 4 TMEM
+          // columns each (B's atoms side by side)
           sf_copy(tmem_base + kColSfa + 4 * j, sf_desc(smem_u32(sm.sfa(s) + 512 * j)));
-          sf_copy(tmem_base + kColSfb + 4 * j, sf_desc(smem_u32(sm.sfb(s) + 512 * j)));
+#pragma unroll
+          for (int a = 0; a < kNAtoms; ++a)
+            sf_copy(tmem_base + kColSfb + 4 * (kNAtoms * j + a),
+                    sf_desc(smem_u32(sm.sfb(s) + a * kSfAtomBytes + 512 * j)));
         }
 #pragma unroll
         for (int j = 0; j < 4; ++j)     // UMMA K = 64 e2m1 = 32 bytes = +2 in 16-byte units
-          umma_nvfp4(tmem_base + b * kTN, adesc + 2 * j, bdesc + 2 * j, idesc,
-                     tmem_base + kColSfa + 4 * j, tmem_base + kColSfb + 4 * j,
+          umma_nvfp4(tmem_base + b * TN, adesc + 2 * j, bdesc + 2 * j, idesc,
+                     tmem_base + kColSfa + 4 * j, tmem_base + kColSfb + 4 * kNAtoms * j,
                      (ks > 0 || j > 0) ? 1u : 0u);
         umma_commit(sm.empty(s));
       }
@@ -214,70 +239,91 @@ nvfp4_gemm_kernel(const __grid_constant__ Args g) {
       ++nunit;
     }
   } else if (warp >= 4) {
-    // ---------------------------------------------------------------- epilogue (8 warps)
+    // ---------------------------------------------------------------- epilogue
     const int ew = warp - 4;
-    const int q = ew & 3, half = ew >> 2;
+    const int q = ew & 3, part = ew >> 2;          // TMEM lane quarter, column part of the tile
     const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
     uint32_t nunit = 0;
     NV41_FP4_FOR_EACH_UNIT(g, mt, nt, e) {
       const float sc = g.a_global * g.b_global[e];
       const long long row = static_cast<long long>(mt) * kTM + q * 32 + lane;
-      const uint32_t b = nunit & 1u, tph = (nunit >> 1) & 1u;
+      const uint32_t b = nunit % kAccBufs, tph = (nunit / kAccBufs) & 1u;
       if (!mbar_wait<40>(sm.tfull(b), tph, sm.abort_flag(), g.status, ST_TIMEOUT_TMEM_FULL)) break;
       tc_fence_after_sync();
+      const uint32_t acc = lane_base + b * TN;
       if (EPI == EPI_SWIGLU_FP4) {
-        // thread = (row, part): gate columns [16 part, +16) and up columns 64 + [16 part, +16)
-        // of the tile -> 16 values of h = one NVFP4 block (`half` runs over 0..3 here: sixteen
-        // epilogue warps).  gate / up are rounded to bf16 first (the dtype the unfused GEMM
-        // stores) so the result equals GEMM -> SwiGLU -> quantizer.
-        uint32_t gv[16], uv[16];
-        tmem_ld_32x32b_x16(lane_base + b * kTN + half * 16, gv);
-        tmem_ld_32x32b_x16(lane_base + b * kTN + 64 + half * 16, uv);
-        tmem_ld_wait_x16(gv);
-        tmem_ld_wait_x16(uv);
+        // thread = (row, part of 4): CW gate columns and the CW up columns TN/2 further on ->
+        // CW values of h = CW/16 NVFP4 blocks.  gate / up are rounded to bf16 first (the dtype
+        // the unfused GEMM stores) so the result equals GEMM -> SwiGLU -> quantizer.
+        constexpr int CW = TN / 8;
+        uint32_t gv[CW], uv[CW];
+        if (CW == 16) {
+          tmem_ld_32x32b_x16(acc + part * CW, reinterpret_cast<uint32_t(&)[16]>(gv));
+          tmem_ld_32x32b_x16(acc + TN / 2 + part * CW, reinterpret_cast<uint32_t(&)[16]>(uv));
+          tmem_ld_wait_x16(reinterpret_cast<uint32_t(&)[16]>(gv));
+          tmem_ld_wait_x16(reinterpret_cast<uint32_t(&)[16]>(uv));
+        } else {
+          tmem_ld_32x32b_x32(acc + part * CW, reinterpret_cast<uint32_t(&)[32]>(gv));
+          tmem_ld_32x32b_x32(acc + TN / 2 + part * CW, reinterpret_cast<uint32_t(&)[32]>(uv));
+          tmem_ld_wait_x32(reinterpret_cast<uint32_t(&)[32]>(gv));
+          tmem_ld_wait_x32(reinterpret_cast<uint32_t(&)[32]>(uv));
+        }
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive(sm.tempty(b));     // accumulator is in registers
         const float w = g.row_weight[row], L = g.limit;
-        const int blk = nt * 4 + half;                 // 16-element block index inside the h row
-        float f[16];
+        const int blk0 = nt * (TN / 32) + part * (CW / 16);   // 16-element block inside the h row
+        uint2 packed[CW / 16];
 #pragma unroll
-        for (int i = 0; i < 16; ++i)
-          f[i] = swiglu_h(__bfloat162float(__float2bfloat16_rn(__uint_as_float(gv[i]) * sc)),
-                          __bfloat162float(__float2bfloat16_rn(__uint_as_float(uv[i]) * sc)), w, L,
-                          g.h_global);
-        uint2 packed;
-        uint8_t sb;
-        nvfp4_block(f, packed, sb, g.h_global == 1.0f);
-        g.h_sf[sf_atom_offset(row, blk, g.h_kpad / 64)] = sb;
-        *reinterpret_cast<uint2*>(g.h_packed + row * (g.h_kpad / 2) + blk * 8) = packed;
+        for (int j = 0; j < CW / 16; ++j) {
+          float f[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i)
+            f[i] = swiglu_h(
+                __bfloat162float(__float2bfloat16_rn(__uint_as_float(gv[j * 16 + i]) * sc)),
+                __bfloat162float(__float2bfloat16_rn(__uint_as_float(uv[j * 16 + i]) * sc)), w, L,
+                g.h_global);
+          uint8_t sb;
+          nvfp4_block(f, packed[j], sb, g.h_global == 1.0f);
+          g.h_sf[sf_atom_offset(row, blk0 + j, g.h_kpad / 64)] = sb;
+        }
+        uint8_t* dst = g.h_packed + row * (g.h_kpad / 2) + blk0 * 8;
+        if (CW == 16)
+          *reinterpret_cast<uint2*>(dst) = packed[0];
+        else
+          *reinterpret_cast<uint4*>(dst) =
+              make_uint4(packed[0].x, packed[0].y, packed[CW / 16 - 1].x, packed[CW / 16 - 1].y);
         ++nunit;
         continue;
       }
-      const int n0 = nt * kTN + half * 64;
-      __nv_bfloat16* dst = g.out + row * g.ld_out + n0;
+      // plain store: thread = (row, half of the tile's columns); the accumulator is copied to
+      // registers and released before the conversion and the stores
+      constexpr int HW = TN / 2;
+      uint32_t v[HW];
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t v[16];
-        tmem_ld_32x32b_x16(lane_base + b * kTN + half * 64 + c * 16, v);
-        tmem_ld_wait_x16(v);
+      for (int c = 0; c < HW / 32; ++c)
+        tmem_ld_32x32b_x32(acc + part * HW + c * 32, reinterpret_cast<uint32_t(&)[32]>(v[c * 32]));
 #pragma unroll
-        for (int i = 0; i < 16; i += 8) {
-          if (n0 + c * 16 + i < g.N) {
-            uint32_t o[4];
-#pragma unroll
-            for (int p = 0; p < 4; ++p) {
-              const __nv_bfloat162 t = __floats2bfloat162_rn(__uint_as_float(v[i + 2 * p]) * sc,
-                                                             __uint_as_float(v[i + 2 * p + 1]) * sc);
-              o[p] = *reinterpret_cast<const uint32_t*>(&t);
-            }
-            *reinterpret_cast<uint4*>(dst + c * 16 + i) = make_uint4(o[0], o[1], o[2], o[3]);
-          }
-        }
-      }
+      for (int c = 0; c < HW / 32; ++c)
+        tmem_ld_wait_x32(reinterpret_cast<uint32_t(&)[32]>(v[c * 32]));
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(sm.tempty(b));
+      const int n0 = nt * TN + part * HW;
+      __nv_bfloat16* dst = g.out + row * g.ld_out + n0;
+#pragma unroll
+      for (int i = 0; i < HW; i += 8) {
+        if (n0 + i < g.N) {
+          uint32_t o[4];
+#pragma unroll
+          for (int p = 0; p < 4; ++p) {
+            const __nv_bfloat162 t = __floats2bfloat162_rn(__uint_as_float(v[i + 2 * p]) * sc,
+                                                           __uint_as_float(v[i + 2 * p + 1]) * sc);
+            o[p] = *reinterpret_cast<const uint32_t*>(&t);
+          }
+          *reinterpret_cast<uint4*>(dst + i) = make_uint4(o[0], o[1], o[2], o[3]);
+        }
+      }
       ++nunit;
     }
   }
@@ -297,14 +343,33 @@ nvfp4_gemm_kernel(const __grid_constant__ Args g) {
 
 using namespace nv41;
 
-static int launch_nvfp4(fp4::Args& g, int epi, const void* a_packed, const void* a_sf,
+template <int EPI, int TN>
+static int launch_variant(const fp4::Args& g, cudaStream_t st) {
+  auto* kern = fp4::nvfp4_gemm_kernel<EPI, TN>;
+  static bool configured = false;        // per instantiation
+  if (!configured) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             fp4::Cfg<TN>::kSmemBytes) != cudaSuccess)
+      return NV41_ERR_CUDA;
+    configured = true;
+  }
+  const long long units = static_cast<long long>(g.n_tiles_m) * g.n_tiles_n;
+  int grid = persistent_grid(sm_count());
+  if (units < grid) grid = static_cast<int>(units);
+  kern<<<grid, EPI == fp4::EPI_SWIGLU_FP4 ? fp4::kThreadsFused : fp4::kThreads,
+         fp4::Cfg<TN>::kSmemBytes, st>>>(g);
+  return launch_status();
+}
+
+// tile_n: 128 or 256 columns per tile
+static int launch_nvfp4(fp4::Args& g, int epi, int tile_n, const void* a_packed, const void* a_sf,
                         float a_global, const void* b_packed, const void* b_sf,
                         const float* b_global, int E, int N, int Kpad, const int* tile_expert,
                         long long P_max, unsigned* status, void* stream) {
   if (!a_packed || !a_sf || !b_packed || !b_sf || !b_global || !tile_expert || !status)
     return NV41_ERR_INVALID;
   if (E <= 0 || N <= 0 || Kpad <= 0 || P_max <= 0 || (P_max % 128) != 0) return NV41_ERR_INVALID;
-  if ((Kpad % 256) != 0 || (N % 128) != 0) return NV41_ERR_UNSUPPORTED;
+  if ((Kpad % 256) != 0 || (N % tile_n) != 0) return NV41_ERR_UNSUPPORTED;
   int rc = make_tmap_2d(&g.tmap_a, a_packed, static_cast<unsigned long long>(P_max), Kpad / 2, 1,
                         128, 128);
   if (rc != NV41_OK) return rc;
@@ -318,25 +383,16 @@ static int launch_nvfp4(fp4::Args& g, int epi, const void* a_packed, const void*
   g.a_global = a_global;
   g.N = N;
   g.n_tiles_m = static_cast<int>(P_max / 128);
-  g.n_tiles_n = N / fp4::kTN;
+  g.n_tiles_n = N / tile_n;
   g.nstage = Kpad / fp4::kStageK;
   g.kgroups = Kpad / 64;
   g.status = status;
-  auto* kern = epi == fp4::EPI_SWIGLU_FP4 ? fp4::nvfp4_gemm_kernel<fp4::EPI_SWIGLU_FP4>
-                                          : fp4::nvfp4_gemm_kernel<fp4::EPI_STORE>;
-  static bool configured[2] = {false, false};
-  if (!configured[epi]) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             fp4::kSmemBytes) != cudaSuccess)
-      return NV41_ERR_CUDA;
-    configured[epi] = true;
-  }
-  const long long units = static_cast<long long>(g.n_tiles_m) * g.n_tiles_n;
-  int grid = persistent_grid(sm_count());
-  if (units < grid) grid = static_cast<int>(units);
-  kern<<<grid, epi == fp4::EPI_SWIGLU_FP4 ? fp4::kThreadsFused : fp4::kThreads, fp4::kSmemBytes,
-         static_cast<cudaStream_t>(stream)>>>(g);
-  return launch_status();
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (epi == fp4::EPI_SWIGLU_FP4)
+    return tile_n == 256 ? launch_variant<fp4::EPI_SWIGLU_FP4, 256>(g, st)
+                         : launch_variant<fp4::EPI_SWIGLU_FP4, 128>(g, st);
+  return tile_n == 256 ? launch_variant<fp4::EPI_STORE, 256>(g, st)
+                       : launch_variant<fp4::EPI_STORE, 128>(g, st);
 }
 
 extern "C" int nv41_moe_gemm_nvfp4(const void* a_packed, const void* a_sf, float a_global,
@@ -345,24 +401,26 @@ extern "C" int nv41_moe_gemm_nvfp4(const void* a_packed, const void* a_sf, float
                                    long long P_max, void* c_out, long long c_ld, unsigned* status,
                                    void* stream) {
   if (!c_out || c_ld < N) return NV41_ERR_INVALID;
-  if ((c_ld % 8) != 0) return NV41_ERR_UNSUPPORTED;
+  if ((c_ld % 8) != 0 || (N % 128) != 0) return NV41_ERR_UNSUPPORTED;
   fp4::Args g;
   memset(&g, 0, sizeof(g));
   g.out = static_cast<__nv_bfloat16*>(c_out);
   g.ld_out = c_ld;
-  return launch_nvfp4(g, fp4::EPI_STORE, a_packed, a_sf, a_global, b_packed, b_sf, b_global, E, N,
-                      Kpad, tile_expert, P_max, status, stream);
+  return launch_nvfp4(g, fp4::EPI_STORE, (N % 256) == 0 ? 256 : 128, a_packed, a_sf, a_global,
+                      b_packed, b_sf, b_global, E, N, Kpad, tile_expert, P_max, status, stream);
 }
 
 extern "C" int nv41_moe_gemm1_nvfp4(const void* a_packed, const void* a_sf, float a_global,
                                     const void* w13_packed, const void* w13_sf,
-                                    const float* w13_global, int E, int I, int Kpad,
-                                    const int* tile_expert, const float* row_weight,
+                                    const float* w13_global, int E, int I, int interleave,
+                                    int Kpad, const int* tile_expert, const float* row_weight,
                                     long long P_max, float swiglu_limit, float h_global,
                                     void* h_packed, void* h_sf, int h_kpad, unsigned* status,
                                     void* stream) {
   if (!row_weight || !h_packed || !h_sf || I <= 0 || !(h_global > 0.f)) return NV41_ERR_INVALID;
-  if ((I % 64) != 0 || h_kpad < I || (h_kpad % 256) != 0) return NV41_ERR_UNSUPPORTED;
+  if ((interleave != 64 && interleave != 128) || (I % interleave) != 0 || h_kpad < I ||
+      (h_kpad % 256) != 0)
+    return NV41_ERR_UNSUPPORTED;
   fp4::Args g;
   memset(&g, 0, sizeof(g));
   g.row_weight = row_weight;
@@ -371,6 +429,7 @@ extern "C" int nv41_moe_gemm1_nvfp4(const void* a_packed, const void* a_sf, floa
   g.h_packed = static_cast<uint8_t*>(h_packed);
   g.h_sf = static_cast<uint8_t*>(h_sf);
   g.h_kpad = h_kpad;
-  return launch_nvfp4(g, fp4::EPI_SWIGLU_FP4, a_packed, a_sf, a_global, w13_packed, w13_sf,
-                      w13_global, E, 2 * I, Kpad, tile_expert, P_max, status, stream);
+  return launch_nvfp4(g, fp4::EPI_SWIGLU_FP4, 2 * interleave, a_packed, a_sf, a_global,
+                      w13_packed, w13_sf, w13_global, E, 2 * I, Kpad, tile_expert, P_max, status,
+                      stream);
 }

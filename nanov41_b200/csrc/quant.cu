@@ -22,36 +22,6 @@
 
 namespace nv41 {
 
-__device__ __forceinline__ void unpack_bf16x8(const uint4& v, float (&f)[8]) {
-  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    f[2 * i] = __uint_as_float(w[i] << 16);
-    f[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
-  }
-}
-
-// Block scale from the block maximum.  fp32 mode: max(amax, 1e-4) * fl32(1/448)
-// (ref/kernel.py:76,80).  ue8m0 mode (the reference's scale_fmt = "ue8m0"): that value rounded
-// up to a power of two, 2^ceil(log2(.)), by the exponent-bit arithmetic of
-// ref/kernel.py:22-37 (fast_log2_ceil / fast_pow2, fast_round_scale).
-__device__ __forceinline__ float block_scale(float amax, int ue8m0) {
-  float s = fmaxf(amax, 1e-4f) * (1.0f / 448.0f);
-  if (ue8m0) {
-    const uint32_t b = __float_as_uint(s);
-    uint32_t e = (b >> 23) & 0xFFu;
-    if (b & 0x7FFFFFu) ++e;
-    s = __uint_as_float(e << 23);
-  }
-  return s;
-}
-
-// e4m3 code of clamp(x / s, +-448), round-to-nearest-even, saturating (r = RN(1 / s)).
-__device__ __forceinline__ uint32_t fp8x4_codes(float a, float b, float c, float d, float s,
-                                                float r) {
-  return e4m3x4_div(a, b, c, d, s, r);
-}
-
 // ------------------------------------------------------------------------- FP8 1x128 rows
 // One quarter-warp (8 lanes x 16 elements) per 1x128 block: lane l holds elements [8l, 8l+8)
 // and [64+8l, 64+8l+8), so both loads of a quarter-warp are one contiguous 128-byte run.  The
@@ -93,10 +63,10 @@ __device__ __forceinline__ void quant_1x128_chunk(const Chunk16& c, unsigned qma
     for (int o = 4; o >= 1; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(qmask, amax, o));
     s = block_scale(amax, kUe8m0);
     const float r = __frcp_rn(s);
-    lo.x = fp8x4_codes(f[0], f[1], f[2], f[3], s, r);
-    lo.y = fp8x4_codes(f[4], f[5], f[6], f[7], s, r);
-    hi.x = fp8x4_codes(g[0], g[1], g[2], g[3], s, r);
-    hi.y = fp8x4_codes(g[4], g[5], g[6], g[7], s, r);
+    lo.x = e4m3x4_div(f[0], f[1], f[2], f[3], s, r);
+    lo.y = e4m3x4_div(f[4], f[5], f[6], f[7], s, r);
+    hi.x = e4m3x4_div(g[0], g[1], g[2], g[3], s, r);
+    hi.y = e4m3x4_div(g[4], g[5], g[6], g[7], s, r);
   } else {
     s = block_scale(__uint_as_float(m << 16), kUe8m0);
     const float r = __frcp_rn(s);
@@ -207,8 +177,8 @@ quant_fp8_128x128_kernel(const __nv_bfloat16* __restrict__ w, int E, int N, int 
     const int rl = p * 16 + r0;
     const int r = nb * 128 + rl;
     uint2 out;
-    out.x = fp8x4_codes(f[p][0], f[p][1], f[p][2], f[p][3], s, rcp);
-    out.y = fp8x4_codes(f[p][4], f[p][5], f[p][6], f[p][7], s, rcp);
+    out.x = e4m3x4_div(f[p][0], f[p][1], f[p][2], f[p][3], s, rcp);
+    out.y = e4m3x4_div(f[p][4], f[p][5], f[p][6], f[p][7], s, rcp);
     if (r < N) {
       *reinterpret_cast<uint2*>(codes + (static_cast<long long>(e) * N + r) * Kpad + col) = out;
     }

@@ -7,6 +7,30 @@
 
 namespace nv41 {
 
+__device__ __forceinline__ void unpack_bf16x8(const uint4& v, float (&f)[8]) {
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    f[2 * i] = __uint_as_float(w[i] << 16);
+    f[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+  }
+}
+
+// Block scale from the block maximum.  fp32 mode: max(amax, 1e-4) * fl32(1/448)
+// (ref/kernel.py:76,80).  ue8m0 mode (the reference's scale_fmt = "ue8m0"): that value rounded
+// up to a power of two, 2^ceil(log2(.)), by the exponent-bit arithmetic of
+// ref/kernel.py:22-37 (fast_log2_ceil / fast_pow2, fast_round_scale).
+__device__ __forceinline__ float block_scale(float amax, int ue8m0) {
+  float s = fmaxf(amax, 1e-4f) * (1.0f / 448.0f);
+  if (ue8m0) {
+    const uint32_t b = __float_as_uint(s);
+    uint32_t e = (b >> 23) & 0xFFu;
+    if (b & 0x7FFFFFu) ++e;
+    s = __uint_as_float(e << 23);
+  }
+  return s;
+}
+
 // Correctly rounded a / s given r = RN(1 / s): a product and two FMA correction steps.  Exact for
 // the quantizers' operand range (s a normal number >= 1e-4/448 scale, |a / s| <= 448 (1 + eps));
 // checked against IEEE division on 4e8 (bf16 a, fp32 s) pairs.  Non-finite or huge |a| take the

@@ -568,7 +568,7 @@ class Nvfp4ExpertWeights:
     E: int
     I: int
     D: int
-    interleaved: bool = False  # w13 rows in 64-row groups gate | up (for the fused gate/up GEMM)
+    interleaved: int = 0       # w13 rows in groups of this many gate | up rows (fused gate/up GEMM)
 
 
 def nvfp4_global_scale(w: torch.Tensor) -> float:
@@ -578,15 +578,19 @@ def nvfp4_global_scale(w: torch.Tensor) -> float:
 
 def quantize_expert_weights_nvfp4(w1, w3, w2, g13: float | None = None,
                                   g2: float | None = None,
-                                  interleave: bool = True) -> Nvfp4ExpertWeights:
+                                  interleave: bool | int = True) -> Nvfp4ExpertWeights:
     """w1, w3: bf16 [E, I, D]; w2: bf16 [E, D, I].  One-off preparation (reads the tensor
-    maxima on the host unless the global scales are given).  With ``interleave`` (needs
-    I % 64 == 0) the rows of W13 are stored [W1[0:64]; W3[0:64]; W1[64:128]; ...] per expert, the
-    order the fused gate/up GEMM reads; otherwise [W1; W3]."""
+    maxima on the host unless the global scales are given).  With ``interleave`` the rows of W13
+    are stored [W1[0:g]; W3[0:g]; W1[g:2g]; ...] per expert, the order the fused gate/up GEMM
+    reads (g = 128 when I % 128 == 0, else 64 when I % 64 == 0; or the value given); otherwise
+    [W1; W3]."""
     E, I, D = w1.shape
-    interleave = interleave and I % 64 == 0
+    if interleave is True:
+        interleave = 128 if I % 128 == 0 else (64 if I % 64 == 0 else 0)
+    interleave = int(interleave)
     if interleave:
-        w13 = torch.cat((w1.reshape(E, I // 64, 64, D), w3.reshape(E, I // 64, 64, D)), dim=2)
+        gsz = interleave
+        w13 = torch.cat((w1.reshape(E, I // gsz, gsz, D), w3.reshape(E, I // gsz, gsz, D)), dim=2)
         w13 = w13.reshape(E * 2 * I, D).contiguous()
     else:
         w13 = torch.cat((w1, w3), dim=1).reshape(E * 2 * I, D).contiguous()
@@ -635,7 +639,7 @@ def gemm1_nvfp4(a_packed, a_sf, a_global: float, wq: Nvfp4ExpertWeights, layout:
     st = status_word(dev)
     check(_lib.load().nv41_moe_gemm1_nvfp4(_ptr(a_packed), _ptr(a_sf), float(a_global),
                                            _ptr(wq.w13_packed), _ptr(wq.w13_sf),
-                                           _ptr(wq.w13_global), wq.E, wq.I, kpad,
+                                           _ptr(wq.w13_global), wq.E, wq.I, wq.interleaved, kpad,
                                            _ptr(layout.tile_expert), _ptr(layout.row_weight), P,
                                            float(limit), float(h_global), _ptr(packed), _ptr(sf),
                                            ipad, _ptr(st), _stream()), "nv41_moe_gemm1_nvfp4")

@@ -83,16 +83,19 @@ def test_forward_nvfp4_vs_oracle(case):
     ops.check_status()
     # the fused gate/up kernel (SwiGLU + NVFP4 re-quantisation in the GEMM epilogue, interleaved
     # W13 rows) must reproduce GEMM -> SwiGLU -> quantizer bit for bit
-    wf = ops.quantize_expert_weights_nvfp4(g["w1"], g["w3"], g["w2"])
-    assert wf.interleaved
-    out_f, parts_f = ops.moe_forward_nvfp4(g["x"], wf, g["weights"], g["indices"], LIMIT,
-                                           return_parts=True)
-    ops.check_status()
     used = int(parts["layout"].meta[1])
-    assert torch.equal(parts_f["h_packed"][:used], parts["h_packed"][:used])
     n_sf = used // 128 * (parts["h_packed"].shape[1] * 2 // 64) * 512
-    assert torch.equal(parts_f["h_sf"][:n_sf], parts["h_sf"][:n_sf])
-    assert torch.equal(out_f, out)
+    for group in (64, 128):                   # 128 x 128 and 128 x 256 tiles
+        if case["I"] % group:
+            continue
+        wf = ops.quantize_expert_weights_nvfp4(g["w1"], g["w3"], g["w2"], interleave=group)
+        assert wf.interleaved == group
+        out_f, parts_f = ops.moe_forward_nvfp4(g["x"], wf, g["weights"], g["indices"], LIMIT,
+                                               return_parts=True)
+        ops.check_status()
+        assert torch.equal(parts_f["h_packed"][:used], parts["h_packed"][:used]), group
+        assert torch.equal(parts_f["h_sf"][:n_sf], parts["h_sf"][:n_sf]), group
+        assert torch.equal(out_f, out), group
     ref, rp = OM.moe_nvfp4(c["x"], c["w1"], c["w3"], c["w2"], c["weights"], c["indices"], LIMIT,
                            g13, g2, return_parts=True)
     pad_pos = parts["layout"].pad_pos.cpu().long()
