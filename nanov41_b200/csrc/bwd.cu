@@ -18,6 +18,7 @@
 #include <cstdint>
 
 #include "../../include/nanov41_b200.h"
+#include "ptx.cuh"
 #include "quant_math.cuh"
 #include "util.cuh"
 
@@ -109,21 +110,30 @@ gather_nvfp4_rows_kernel(const uint8_t* __restrict__ packed, const uint8_t* __re
   }
 }
 
-__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
-  uint32_t o[4];
+// e4m3 codes + block scale of eight bf16 values (a uint4 of four bf16 pairs) whose 1x128 block
+// has the absolute-maximum bit pattern `amax_bits` (act_quant arithmetic, as quant.cu): the
+// packed correctly rounded division when every element of the block is finite, the IEEE
+// division otherwise.
+__device__ __forceinline__ uint2 quant_bf16x8(const uint4& v, uint32_t amax_bits, int ue8m0,
+                                              float& s) {
+  if (amax_bits >= 0x7F80u) {          // inf / NaN somewhere in the block
+    float f[8];
+    unpack_bf16x8(v, f);
+    float amax = 0.f;                  // fmaxf drops NaNs, as the standalone quantizer does
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const __nv_bfloat162 b = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
-    o[i] = *reinterpret_cast<const uint32_t*>(&b);
+    for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(f[i]));
+    const unsigned hmask = 0xFFFFu << (threadIdx.x & 16);
+#pragma unroll
+    for (int o = 8; o >= 1; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(hmask, amax, o));
+    s = block_scale(amax, ue8m0);
+    const float r = __frcp_rn(s);
+    return make_uint2(e4m3x4_div(f[0], f[1], f[2], f[3], s, r),
+                      e4m3x4_div(f[4], f[5], f[6], f[7], s, r));
   }
-  return make_uint4(o[0], o[1], o[2], o[3]);
-}
-__device__ __forceinline__ uint2 quant8(const float (&f)[8], float s) {
+  s = block_scale(__uint_as_float(amax_bits << 16), ue8m0);
   const float r = __frcp_rn(s);
-  return make_uint2(e4m3x4_div(f[0], f[1], f[2], f[3], s, r),
-                    e4m3x4_div(f[4], f[5], f[6], f[7], s, r));
+  return e4m3x8_div_bf16(v, f32x2_pack(-s, -s), f32x2_pack(r, r));
 }
-
 
 // One warp per padded row; a half-warp (16 lanes x 8 columns) covers one 1x128 block.
 __global__ void __launch_bounds__(256)
@@ -153,40 +163,53 @@ swiglu_bwd_quant_kernel(const __nv_bfloat16* __restrict__ dact, const __nv_bfloa
         unpack_bf16x8(__ldg(reinterpret_cast<const uint4*>(gate + p * I + col)), g);
         unpack_bf16x8(__ldg(reinterpret_cast<const uint4*>(up + p * I + col)), u);
       }
-      float am_g = 0.f, am_u = 0.f;
+      // dgate / dup are rounded to bf16 as they are produced (the quantizer sees the stored
+      // bf16 values); the block maxima are taken on the bf16 bit patterns (quant.cu does the same)
+      uint32_t pg[4], pu[4];
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        float gc = g[i], uc = u[i];
-        bool mg = true, mu = true;
-        if (L > 0.f) {
-          gc = fminf(gc, L);
-          uc = fminf(fmaxf(uc, -L), L);
-          mg = gc < L;
-          mu = fabsf(uc) < L;
+      for (int i = 0; i < 4; ++i) {
+        float dgf[2], duf[2];
+#pragma unroll
+        for (int t = 0; t < 2; ++t) {
+          float gc = g[2 * i + t], uc = u[2 * i + t];
+          bool mg = true, mu = true;
+          if (L > 0.f) {
+            gc = fminf(gc, L);
+            uc = fminf(fmaxf(uc, -L), L);
+            mg = gc < L;
+            mu = fabsf(uc) < L;
+          }
+          const float sig = fmaf(0.5f, tanh_approx(0.5f * gc), 0.5f);   // sigmoid by hardware tanh
+          const float silu = gc * sig;
+          const float dsilu = sig * fmaf(gc, 1.f - sig, 1.f);
+          const float dw = d[2 * i + t] * w;
+          dws_acc = fmaf(d[2 * i + t], silu * uc, dws_acc);
+          dgf[t] = mg ? dw * uc * dsilu : 0.f;
+          duf[t] = mu ? dw * silu : 0.f;
         }
-        const float sig = 1.f / (1.f + __expf(-gc));
-        const float silu = gc * sig;
-        const float dsilu = sig * (1.f + gc * (1.f - sig));
-        const float dw = d[i] * w;
-        dws_acc = fmaf(d[i], silu * uc, dws_acc);
-        // round to bf16 first: the quantizer sees the stored bf16 values
-        dg[i] = __bfloat162float(__float2bfloat16_rn(mg ? dw * uc * dsilu : 0.f));
-        du[i] = __bfloat162float(__float2bfloat16_rn(mu ? dw * silu : 0.f));
-        am_g = fmaxf(am_g, fabsf(dg[i]));
-        am_u = fmaxf(am_u, fabsf(du[i]));
+        const __nv_bfloat162 bg = __floats2bfloat162_rn(dgf[0], dgf[1]);
+        const __nv_bfloat162 bu = __floats2bfloat162_rn(duf[0], duf[1]);
+        pg[i] = *reinterpret_cast<const uint32_t*>(&bg);
+        pu[i] = *reinterpret_cast<const uint32_t*>(&bu);
       }
+      const uint32_t M = 0x7FFF7FFFu;
+      uint32_t bm_g = __vmaxu2(__vmaxu2(pg[0] & M, pg[1] & M), __vmaxu2(pg[2] & M, pg[3] & M));
+      uint32_t bm_u = __vmaxu2(__vmaxu2(pu[0] & M, pu[1] & M), __vmaxu2(pu[2] & M, pu[3] & M));
+      bm_g = max(bm_g & 0xFFFFu, bm_g >> 16);
+      bm_u = max(bm_u & 0xFFFFu, bm_u >> 16);
 #pragma unroll
       for (int o = 8; o >= 1; o >>= 1) {
-        am_g = fmaxf(am_g, __shfl_xor_sync(hmask, am_g, o));
-        am_u = fmaxf(am_u, __shfl_xor_sync(hmask, am_u, o));
+        bm_g = max(bm_g, __shfl_xor_sync(hmask, bm_g, o));
+        bm_u = max(bm_u, __shfl_xor_sync(hmask, bm_u, o));
       }
       if (in) {
-        const float sg = block_scale(am_g, ue8m0);
-        const float su = block_scale(am_u, ue8m0);
-        *reinterpret_cast<uint4*>(dgate + p * I + col) = pack8(dg);
-        *reinterpret_cast<uint4*>(dup + p * I + col) = pack8(du);
-        *reinterpret_cast<uint2*>(codes + p * 2 * I + col) = quant8(dg, sg);
-        *reinterpret_cast<uint2*>(codes + p * 2 * I + I + col) = quant8(du, su);
+        const uint4 vg = make_uint4(pg[0], pg[1], pg[2], pg[3]);
+        const uint4 vu = make_uint4(pu[0], pu[1], pu[2], pu[3]);
+        *reinterpret_cast<uint4*>(dgate + p * I + col) = vg;
+        *reinterpret_cast<uint4*>(dup + p * I + col) = vu;
+        float sg, su;
+        *reinterpret_cast<uint2*>(codes + p * 2 * I + col) = quant_bf16x8(vg, bm_g, ue8m0, sg);
+        *reinterpret_cast<uint2*>(codes + p * 2 * I + I + col) = quant_bf16x8(vu, bm_u, ue8m0, su);
         if ((lane & 15) == 0) {
           const int kb = col / 128;
           scales[static_cast<long long>(kb) * P_max + p] = sg;

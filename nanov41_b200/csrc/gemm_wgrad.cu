@@ -35,7 +35,9 @@ constexpr int kBBytes = (kTN / 64) * kBox;        // 32 KiB
 constexpr int kStageBytes = kABytes + kBBytes;
 constexpr int kStages = 4;
 constexpr int kThreads = 384;
-constexpr int kSmemBytes = kStages * kStageBytes + (2 * kStages + 4) * 8 + 16 + 1024;
+constexpr int kMaxExperts = 1024;        // size of the in-kernel expert order table
+constexpr int kSmemBytes =
+    kStages * kStageBytes + (2 * kStages + 4) * 8 + 16 + kMaxExperts * 4 + 1024;
 
 struct Args {
   CUtensorMap tmap_a;            // [P_max, M] bf16, box 64 x 64
@@ -57,21 +59,43 @@ struct Smem {
   __device__ uint64_t* tempty(int b) const { return bars() + 2 * kStages + 2 + b; }
   __device__ uint32_t* tmem_slot() const { return reinterpret_cast<uint32_t*>(bars() + 2 * kStages + 4); }
   __device__ volatile uint32_t* abort_flag() const { return tmem_slot() + 1; }
+  __device__ int* order() const { return reinterpret_cast<int*>(tmem_slot() + 4); }   // [E]
 };
 
+// Work units are (expert, output tile); a unit costs its expert's K steps.  Experts are ranked by
+// row count (descending, ties by index: every CTA computes the same table), units are numbered
+// expert-major in that order, and CTA c takes units c, 2G-1-c, 2G+c, 4G-1-c, ... (G = grid): the
+// snake over a descending sequence keeps the CTAs' totals within about one unit of each other
+// under skewed routing, and the tiles of one expert run at the same time on neighbouring CTAs,
+// so its rows are fetched into L2 once.
 struct Unit {
   int e, mt, nt, ksteps, row0;
 };
-__device__ __forceinline__ Unit decode(const Args& g, int u) {
+__device__ __forceinline__ Unit decode(const Args& g, const int* order, int u) {
   Unit r;
-  r.e = u % g.E;
-  const int t = u / g.E;
+  const int tiles = g.tiles_m * g.tiles_n;
+  const int rank = u / tiles, t = u - rank * tiles;
+  r.e = order[rank];
   r.mt = t / g.tiles_n;
   r.nt = t - r.mt * g.tiles_n;
   r.row0 = g.pad_off[r.e];
   r.ksteps = (g.pad_off[r.e + 1] - r.row0) / kKS;
   return r;
 }
+struct UnitIter {
+  int round = 0;
+  // next unit of this CTA, or -1
+  __device__ int next(int total) {
+    const int grid = static_cast<int>(gridDim.x), c = static_cast<int>(blockIdx.x);
+    for (;;) {
+      const long long base = static_cast<long long>(round) * grid;
+      if (base >= total) return -1;
+      const int pos = (round & 1) ? grid - 1 - c : c;
+      ++round;
+      if (base + pos < total) return static_cast<int>(base + pos);
+    }
+  }
+};
 
 __global__ void __launch_bounds__(kThreads, 1) wgrad_kernel(const __grid_constant__ Args g) {
   extern __shared__ uint8_t smem_raw[];
@@ -97,6 +121,17 @@ __global__ void __launch_bounds__(kThreads, 1) wgrad_kernel(const __grid_constan
     tmem_alloc(sm.tmem_slot(), 512);
     tmem_relinquish();
   }
+  // rank of every expert by padded rows, descending
+  int* order = sm.order();
+  for (int e = threadIdx.x; e < g.E; e += blockDim.x) {
+    const int rows = g.pad_off[e + 1] - g.pad_off[e];
+    int rank = 0;
+    for (int o = 0; o < g.E; ++o) {
+      const int ro = g.pad_off[o + 1] - g.pad_off[o];
+      rank += (ro > rows || (ro == rows && o < e)) ? 1 : 0;
+    }
+    order[rank] = e;
+  }
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
@@ -106,8 +141,9 @@ __global__ void __launch_bounds__(kThreads, 1) wgrad_kernel(const __grid_constan
   if (warp == 0 && lane == 0) {
     // ---------------------------------------------------------------- TMA producer
     uint32_t it = 0;
-    for (int u = blockIdx.x; u < total; u += gridDim.x) {
-      const Unit un = decode(g, u);
+    UnitIter iter;
+    for (int u = iter.next(total); u >= 0; u = iter.next(total)) {
+      const Unit un = decode(g, order, u);
       for (int ks = 0; ks < un.ksteps; ++ks, ++it) {
         const int s = it % kStages;
         const uint32_t ph = (it / kStages) & 1u;
@@ -127,8 +163,9 @@ __global__ void __launch_bounds__(kThreads, 1) wgrad_kernel(const __grid_constan
     // ---------------------------------------------------------------- UMMA issuer
     constexpr uint32_t idesc = umma_idesc(kTM, kTN, 1, 1, 1, 1);   // bf16 x bf16, both MN-major
     uint32_t it = 0, nunit = 0;
-    for (int u = blockIdx.x; u < total; u += gridDim.x) {
-      const Unit un = decode(g, u);
+    UnitIter iter;
+    for (int u = iter.next(total); u >= 0; u = iter.next(total)) {
+      const Unit un = decode(g, order, u);
       if (un.ksteps == 0) continue;       // empty expert: the epilogue writes zeros by itself
       const uint32_t b = nunit & 1u, tph = (nunit >> 1) & 1u;
       if (!mbar_wait(sm.tempty(b), tph ^ 1u, sm.abort_flag(), g.status, ST_TIMEOUT_TMEM_EMPTY))
@@ -163,8 +200,9 @@ __global__ void __launch_bounds__(kThreads, 1) wgrad_kernel(const __grid_constan
     const int q = ew & 3, half = ew >> 2;
     const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
     uint32_t nunit = 0;
-    for (int u = blockIdx.x; u < total; u += gridDim.x) {
-      const Unit un = decode(g, u);
+    UnitIter iter;
+    for (int u = iter.next(total); u >= 0; u = iter.next(total)) {
+      const Unit un = decode(g, order, u);
       const int m = un.mt * kTM + q * 32 + lane;
       const int n0 = un.nt * kTN + half * 128;
       __nv_bfloat16* dst = g.out + (static_cast<long long>(un.e) * g.M + m) * g.N + n0;
@@ -230,7 +268,7 @@ extern "C" int nv41_moe_wgrad_bf16(const void* a_rows, const void* b_rows, const
   if (!a_rows || !b_rows || !pad_off || !out || !status || E <= 0 || M <= 0 || N <= 0 ||
       P_max <= 0 || (P_max % 128) != 0)
     return NV41_ERR_INVALID;
-  if ((M % 8) != 0 || (N % 8) != 0) return NV41_ERR_UNSUPPORTED;
+  if ((M % 8) != 0 || (N % 8) != 0 || E > wgrad::kMaxExperts) return NV41_ERR_UNSUPPORTED;
   wgrad::Args g;
   memset(&g, 0, sizeof(g));
   int rc = make_tmap_2d(&g.tmap_a, a_rows, static_cast<unsigned long long>(P_max), M, 2, 64, 64);
