@@ -133,8 +133,7 @@ __global__ void __launch_bounds__(256)
 quant_fp8_128x128_kernel(const __nv_bfloat16* __restrict__ w, int E, int N, int K, int Kpad,
                          int Npad, uint8_t* __restrict__ codes, uint8_t* __restrict__ codes_t,
                          float* __restrict__ scales, int ue8m0) {
-  __shared__ float red[8];
-  __shared__ float s_scale;
+  __shared__ uint32_t red[8];
   __shared__ __align__(16) uint8_t tile[128][128 + 16];
   const int kb = blockIdx.x, nb = blockIdx.y, e = blockIdx.z;
   const int nkb = Kpad / 128, nnb = (N + 127) / 128;
@@ -142,43 +141,65 @@ quant_fp8_128x128_kernel(const __nv_bfloat16* __restrict__ w, int E, int N, int 
   const int chunk = tid & 15;          // 16 chunks of 8 elements across the 128 columns
   const int r0 = tid >> 4;             // 16 rows per pass, 8 passes
   const int col = kb * 128 + chunk * 8;
-  float f[8][8];
-  float amax = 0.f;
+  // the block stays in registers as bf16 pairs; its maximum is taken on the bit patterns
+  uint4 v[8];
+  uint32_t bm = 0u;
+  const uint32_t M = 0x7FFF7FFFu;
 #pragma unroll
   for (int p = 0; p < 8; ++p) {
     const int r = nb * 128 + p * 16 + r0;
+    v[p] = make_uint4(0u, 0u, 0u, 0u);
+    if (r < N && col < K)
+      v[p] = __ldg(reinterpret_cast<const uint4*>(w + (static_cast<long long>(e) * N + r) * K + col));
+    bm = __vmaxu2(bm, __vmaxu2(__vmaxu2(v[p].x & M, v[p].y & M), __vmaxu2(v[p].z & M, v[p].w & M)));
+  }
+  bm = max(bm & 0xFFFFu, bm >> 16);
 #pragma unroll
-    for (int i = 0; i < 8; ++i) f[p][i] = 0.f;
-    if (r < N && col < K) {
-      const uint4 v = __ldg(reinterpret_cast<const uint4*>(
-          w + (static_cast<long long>(e) * N + r) * K + col));
-      unpack_bf16x8(v, f[p]);
+  for (int o = 16; o >= 1; o >>= 1) bm = max(bm, __shfl_xor_sync(0xFFFFFFFFu, bm, o));
+  if ((tid & 31) == 0) red[tid >> 5] = bm;
+  __syncthreads();
+  bm = red[0];
+#pragma unroll
+  for (int i = 1; i < 8; ++i) bm = max(bm, red[i]);
+  const bool finite = bm < 0x7F80u;
+  float s;
+  if (finite) {
+    s = block_scale(__uint_as_float(bm << 16), ue8m0);
+  } else {                             // inf / NaN in the block: float maximum (NaNs dropped)
+    float amax = 0.f;
+#pragma unroll
+    for (int p = 0; p < 8; ++p) {
+      float f[8];
+      unpack_bf16x8(v[p], f);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(f[i]));
     }
 #pragma unroll
-    for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(f[p][i]));
-  }
+    for (int o = 16; o >= 1; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
+    __shared__ float redf[8];
+    if ((tid & 31) == 0) redf[tid >> 5] = amax;
+    __syncthreads();
+    amax = redf[0];
 #pragma unroll
-  for (int o = 16; o >= 1; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
-  if ((tid & 31) == 0) red[tid >> 5] = amax;
-  __syncthreads();
-  if (tid == 0) {
-    float m = red[0];
-#pragma unroll
-    for (int i = 1; i < 8; ++i) m = fmaxf(m, red[i]);
-    const float s = block_scale(m, ue8m0);
-    s_scale = s;
-    scales[(static_cast<long long>(e) * nnb + nb) * nkb + kb] = s;
+    for (int i = 1; i < 8; ++i) amax = fmaxf(amax, redf[i]);
+    s = block_scale(amax, ue8m0);
   }
-  __syncthreads();
-  const float s = s_scale;
+  if (tid == 0) scales[(static_cast<long long>(e) * nnb + nb) * nkb + kb] = s;
   const float rcp = __frcp_rn(s);
+  const uint64_t ns2 = f32x2_pack(-s, -s), r2 = f32x2_pack(rcp, rcp);
 #pragma unroll
   for (int p = 0; p < 8; ++p) {
     const int rl = p * 16 + r0;
     const int r = nb * 128 + rl;
     uint2 out;
-    out.x = e4m3x4_div(f[p][0], f[p][1], f[p][2], f[p][3], s, rcp);
-    out.y = e4m3x4_div(f[p][4], f[p][5], f[p][6], f[p][7], s, rcp);
+    if (finite) {
+      out = e4m3x8_div_bf16(v[p], ns2, r2);
+    } else {
+      float f[8];
+      unpack_bf16x8(v[p], f);
+      out.x = e4m3x4_div(f[0], f[1], f[2], f[3], s, rcp);
+      out.y = e4m3x4_div(f[4], f[5], f[6], f[7], s, rcp);
+    }
     if (r < N) {
       *reinterpret_cast<uint2*>(codes + (static_cast<long long>(e) * N + r) * Kpad + col) = out;
     }
@@ -186,24 +207,31 @@ quant_fp8_128x128_kernel(const __nv_bfloat16* __restrict__ w, int E, int N, int 
   }
   if (codes_t) {
     __syncthreads();
-    // transposed store: thread -> (k-row = tid/2 within the block, 64 n-values = half a row)
-    const int kr = tid >> 1, nh = (tid & 1) * 64;
-    const long long krow = static_cast<long long>(e) * Kpad + kb * 128 + kr;
+    // transposed store: thread -> (4 k-rows, 16 n-values): sixteen 32-bit reads of the tile
+    // (lanes along k: conflict-free), four 4x4 byte transposes, four 16-byte stores
+    const int k4 = tid & 31, n16 = tid >> 5;
+    uint32_t rows[4][4];               // [k-row within the 4][word of 4 n-values]
 #pragma unroll
-    for (int c = 0; c < 4; ++c) {
-      uint32_t wds[4];
+    for (int j = 0; j < 4; ++j) {
+      uint32_t a[4];
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        uint32_t wd = 0;
+      for (int b = 0; b < 4; ++b)
+        a[b] = *reinterpret_cast<const uint32_t*>(&tile[n16 * 16 + j * 4 + b][k4 * 4]);
+      // a[b] = codes of n = 4j + b at k = 4 k4 .. +3; rows[kk][j] = bytes kk of a[0..3]
+      const uint32_t t0 = __byte_perm(a[0], a[1], 0x5140), t1 = __byte_perm(a[2], a[3], 0x5140);
+      const uint32_t t2 = __byte_perm(a[0], a[1], 0x7362), t3 = __byte_perm(a[2], a[3], 0x7362);
+      rows[0][j] = __byte_perm(t0, t1, 0x5410);
+      rows[1][j] = __byte_perm(t0, t1, 0x7632);
+      rows[2][j] = __byte_perm(t2, t3, 0x5410);
+      rows[3][j] = __byte_perm(t2, t3, 0x7632);
+    }
+    const int n = nb * 128 + n16 * 16;
+    if (n < Npad) {
 #pragma unroll
-        for (int b = 0; b < 4; ++b)
-          wd |= static_cast<uint32_t>(tile[nh + c * 16 + j * 4 + b][kr]) << (8 * b);
-        wds[j] = wd;
-      }
-      const int n = nb * 128 + nh + c * 16;
-      if (n < Npad) {
+      for (int kk = 0; kk < 4; ++kk) {
+        const long long krow = static_cast<long long>(e) * Kpad + kb * 128 + k4 * 4 + kk;
         *reinterpret_cast<uint4*>(codes_t + krow * Npad + n) =
-            make_uint4(wds[0], wds[1], wds[2], wds[3]);
+            make_uint4(rows[kk][0], rows[kk][1], rows[kk][2], rows[kk][3]);
       }
     }
   }
