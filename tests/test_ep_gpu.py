@@ -76,6 +76,14 @@ def _worker(rank, world, port):
                 want = ops.moe_forward_fp8(xs, wa, g["weights"][sl], g["indices"][sl], 10.0, shared)
                 ops.check_status()
                 assert torch.equal(got, want), ue8m0
+            # skewed routing: rank 1 sends every row to rank 0's experts (its own run and rank
+            # 0's run in rank 1's buffers are the extreme cases: empty / everything)
+            idx_skew = g["indices"][sl] % (CASE["E"] // world) if rank == 1 else g["indices"][sl]
+            got = ep.moe_forward_fp8_seg(seg, x2, wl, g["weights"][sl], idx_skew, CASE["E"], 10.0,
+                                         shared, slice_rows=256)
+            want = ops.moe_forward_fp8(x2, wa, g["weights"][sl], idx_skew, 10.0, shared)
+            ops.check_status()
+            assert torch.equal(got, want), ("skew", ue8m0)
             seg.close()
         ref = OM.moe_fp8(c["x"][sl], c["w1"], c["w3"], c["w2"], c["weights"][sl], c["indices"][sl],
                          10.0, shared=shared.cpu())
