@@ -83,6 +83,32 @@ class PipelinedE2E:
                 main.wait_event(ev)
 
 
+def capture_graph(step, reset=None):
+    """Capture one call of ``step`` (kernel launches only, static shapes and buffers) in a CUDA
+    graph and return (replay callable, True); on any capture error return (step, False).
+    ``reset`` runs between the warm-up on a side stream and the capture (e.g. drop .grad)."""
+    try:
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(3):
+                step()
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        if reset is not None:
+            reset()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            step()
+        torch.cuda.synchronize()
+        return graph.replay, True
+    except Exception as exc:                       # noqa: BLE001 - any capture failure: run eagerly
+        print(f"[bench] CUDA graph capture failed ({type(exc).__name__}: {exc}); running eagerly",
+              file=sys.stderr, flush=True)
+        torch.cuda.synchronize()
+        return step, False
+
+
 class ClockSampler:
     """Samples nvidia-smi clocks / throttle reasons every 200 ms while the timed region runs."""
     Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
@@ -373,6 +399,11 @@ def run_stack(args, name):
                                                  c["w3"], c["w2"], LIMIT)
                 y.backward(c["x"].detach())
         flops, launches = 3.0 * fwd, 26 * L
+
+        def reset():
+            for c in layers:
+                for n in ("x", "w1", "w3", "w2", "weights"):
+                    c[n].grad = None
     else:
         wqs = [ops.quantize_expert_weights_nvfp4(c["w1"], c["w3"], c["w2"]) for c in layers]
 
@@ -380,6 +411,10 @@ def run_stack(args, name):
             for c, w in zip(layers, wqs):
                 ops.moe_forward_nvfp4(c["x"], w, c["weights"], c["indices"], LIMIT)
         flops, launches = fwd, 9 * L
+        reset = None
+    graphed = False
+    if args.cuda_graph:
+        step, graphed = capture_graph(step, reset)
     for _ in range(args.warmup):
         step()
     torch.cuda.synchronize()
@@ -397,7 +432,8 @@ def run_stack(args, name):
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": st["mode"], "data": "synthetic",
         "config": {"workload": f"{name}: routed experts of the {L} MoE layers, {T} tokens, D={D} "
-                               f"I={I} E={E} top-{k}, uniform routing", **st},
+                               f"I={I} E={E} top-{k}, uniform routing", **st,
+                   "cuda_graph": graphed},
         "moe_layer_tokens_per_s": T / (ms * 1e-3), "gpu_launches": launches * args.steps}),
         flush=True)
 
@@ -431,6 +467,10 @@ def run_ours(args):
 
     def step_device():
         return ops.moe_forward_fp8(g["x"], wq, g["weights"], g["indices"], LIMIT)
+
+    graphed = False
+    if args.cuda_graph and world == 1:
+        step_device, graphed = capture_graph(step_device)
 
     step_e2e = PipelinedE2E((x_host, w_host, idx_host),
                             lambda xd, wd, idd: ops.moe_forward_fp8(xd, wq, wd, idd, LIMIT),
@@ -565,7 +605,8 @@ def run_ours(args):
         "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms_dev, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "fp8_e4m3 (fp32 accumulate, bf16 out)", "data": "synthetic",
-        "config": dict(workload_config(), parallelism=f"replicas x{world}" if world > 1 else "1 GPU"),
+        "config": dict(workload_config(), parallelism=f"replicas x{world}" if world > 1 else "1 GPU",
+                       cuda_graph=graphed),
         "e2e": {"value": world * flops / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s",
                 "ms_per_step": ms_e2e, "h2d_bytes_per_step": bytes_in,
                 "d2h_bytes_per_step": out_host.numel() * 2,
@@ -616,6 +657,8 @@ def main():
                     help="peer mode: runs of the owner's row space whose pull / push overlap the GEMMs")
     ap.add_argument("--ep-copy-sms", type=int, default=0,
                     help="peer mode with slices: SMs the GEMM grids leave to the pull / push kernels")
+    ap.add_argument("--cuda-graph", type=int, default=1,
+                    help="1 GPU: replay the device-resident step from a CUDA graph (0 = launch eagerly)")
     ap.add_argument("--workload", default="c2", choices=["c2", "d8", "d12"],
                     help="c2 = BASELINE config 2 (headline); d8 / d12 = expert stacks of configs 3 / 4")
     ap.add_argument("--scale-fmt", default="fp32", choices=["fp32", "ue8m0"],
