@@ -1,19 +1,24 @@
-"""Expert parallelism: experts sharded contiguously over the ranks of a process group, tokens
-data-parallel, one variable-size all-to-all each way (NCCL over NVLink through
-``torch.distributed``).
+"""Expert parallelism on one node: experts sharded contiguously over the ranks of a process
+group (rank r owns experts [r*E/G, (r+1)*E/G), the reference's own
+``experts_start_idx = rank * n_local_experts`` convention), tokens data-parallel.
 
 The reference only has the replicate-tokens + fp32 ``all_reduce(y)`` scheme of the official
 inference code (nanov41/_ref_patched_model.py:880-887,918-919; mirrored nanov41/fast_moe.py:
 446-450,468-471), which moves T*D*4 bytes per rank whatever the routing.  Here every routed row
-travels once: rank r owns experts [r*E/G, (r+1)*E/G) (the reference's own
-``experts_start_idx = rank * n_local_experts`` convention), rows are quantised to FP8 *before*
-they are sent (codes + 1x128 scales: 2,112 B per row at D = 2048 instead of 4,096), the owner
-runs the grouped FP8 GEMMs on what it received, and bf16 results come back to the token's home
-rank, where the top-k sum (+ shared expert) is done in fp32 with a single rounding.
+travels once each way, as FP8 codes + 1x128 scales out (quantised BEFORE it is sent: 2,112 B
+per row at D = 2048 instead of 4,096) and as a bf16 result back; the top-k sum (+ shared expert)
+is done at the token's home rank in fp32 with a single rounding.  Three transports, same
+signature and bit-identical results:
 
-Per layer and direction: one all-to-all of the per-peer row counts (the only host
-synchronisation: NCCL's variable-size all-to-all takes host-side split sizes) and one
-all-to-all per payload tensor.  Received rows land in local HBM before any kernel touches them.
+``moe_forward_fp8_seg``   (default) rows stay in the home rank's expert-major layout inside
+                          CUDA-IPC-mapped buffers; the owner copies its contiguous run of tiles
+                          with the copy engines, so no SM and no pack / unpack pass is spent on
+                          communication.  ``ep_autograd`` builds the training path on it.
+``moe_forward_fp8_peer``  the owner's kernels pull rows from / push rows to peer-mapped buffers
+                          (plain loads / stores, or bulk-copy movers on reserved SMs).
+``moe_forward_fp8_ep``    NCCL ``all_to_all_single`` with variable splits of packed rows.
+
+No kernel waits on another rank; ordering comes from small collectives in stream order.
 """
 from __future__ import annotations
 
