@@ -48,20 +48,43 @@ gather_fp8_rows_kernel(const uint8_t* __restrict__ codes, long long ld, const fl
                        long long s_kb_stride, const int* __restrict__ row_token,
                        const int* __restrict__ meta, int K, uint8_t* __restrict__ codes_rows,
                        float* __restrict__ scales_rows, long long P_max, uint8_t* __restrict__ atoms) {
+  // A warp owns 32 consecutive padded rows: the codes are copied four rows at a time (every
+  // lane has up to eight 16-byte loads in flight), then lane = row for the scales, so that each
+  // k-block's 32 scales are one 128-byte store.
   const int lane = threadIdx.x & 31;
   const long long warp0 = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
   const long long nwarps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
-  const long long used = meta[1];
+  const long long used = meta[1];                       // a multiple of 128
   const int nkb = K / 128, chunks = K / 16;
-  for (long long p = warp0; p < used; p += nwarps) {
-    const int tok = row_token[p];
-    for (int c = lane; c < chunks; c += 32) {
-      uint4 v = make_uint4(0u, 0u, 0u, 0u);
-      if (tok >= 0) v = __ldg(reinterpret_cast<const uint4*>(codes + tok * ld) + c);
-      reinterpret_cast<uint4*>(codes_rows + p * K)[c] = v;
+  for (long long p0 = warp0 * 32; p0 < used; p0 += nwarps * 32) {
+    const int my_tok = row_token[p0 + lane];
+    for (int r4 = 0; r4 < 32; r4 += 4) {
+      int tok[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) tok[u] = __shfl_sync(0xFFFFFFFFu, my_tok, r4 + u);
+      for (int c0 = 0; c0 < chunks; c0 += 64) {
+        uint4 v[4][2];
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+#pragma unroll
+          for (int j = 0; j < 2; ++j) {
+            const int c = c0 + j * 32 + lane;
+            v[u][j] = make_uint4(0u, 0u, 0u, 0u);
+            if (tok[u] >= 0 && c < chunks)
+              v[u][j] = __ldg(reinterpret_cast<const uint4*>(codes + tok[u] * ld) + c);
+          }
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+#pragma unroll
+          for (int j = 0; j < 2; ++j) {
+            const int c = c0 + j * 32 + lane;
+            if (c < chunks) reinterpret_cast<uint4*>(codes_rows + (p0 + r4 + u) * K)[c] = v[u][j];
+          }
+      }
     }
-    for (int kb = lane; kb < nkb; kb += 32) {
-      const float s = tok >= 0 ? __ldg(scales + kb * s_kb_stride + tok) : 1.0f;
+    const long long p = p0 + lane;
+    for (int kb = 0; kb < nkb; ++kb) {
+      const float s = my_tok >= 0 ? __ldg(scales + kb * s_kb_stride + my_tok) : 1.0f;
       scales_rows[kb * P_max + p] = s;
       if (atoms) {
         const uint32_t byte = (__float_as_uint(s) >> 23) & 0xFFu;
@@ -247,8 +270,8 @@ extern "C" int nv41_gather_fp8_rows(const void* codes, long long ld, const float
   if (!codes || !scales_kmajor || !row_token || !meta || !codes_rows || !scales_rows_kmajor ||
       K <= 0 || (K % 128) != 0 || P_max <= 0 || (P_max % 128) != 0 || ld < K || (ld % 16) != 0)
     return NV41_ERR_INVALID;
-  long long blocks = (P_max + 7) / 8;
-  if (blocks > 148LL * 16) blocks = 148LL * 16;
+  long long blocks = (P_max / 32 + 7) / 8;            // one warp per 32 rows
+  if (blocks > 148LL * 8) blocks = 148LL * 8;
   gather_fp8_rows_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const uint8_t*>(codes), ld, scales_kmajor, scale_kb_stride, row_token, meta, K,
       static_cast<uint8_t*>(codes_rows), scales_rows_kmajor, P_max, static_cast<uint8_t*>(sf_atoms));
