@@ -17,11 +17,29 @@ from . import ops
 from .workloads import make_case
 
 
+def backward_case(tokens: int, experts: int):
+    c = make_case(T=tokens, E=experts, k=6, D=1024, I=1024, seed=1)
+    g = {n: t.cuda() for n, t in c.items()}
+    lay = ops.build_layout(g["indices"].reshape(-1), experts, 6, g["weights"].reshape(-1))
+    a = torch.randn(lay.P_max, 1024, device="cuda").bfloat16()
+    b = torch.randn(lay.P_max, 1024, device="cuda").bfloat16()
+    ops.quantize_expert_weights(g["w1"], g["w3"], g["w2"], transposed=True)
+    ops.swiglu_bwd_quant(a, b, a, lay, 10.0)
+    out = ops.wgrad_bf16(a, b, lay)
+    ops.check_status()
+    print("profile_case backward ok", float(out.float().abs().mean()), lay.counts.tolist())
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--tokens", type=int, default=4096)
     ap.add_argument("--experts", type=int, default=16)
+    ap.add_argument("--backward", action="store_true",
+                    help="run the backward kernels instead (weight quantizer with transposed copy, "
+                         "SwiGLU backward + quantisation, weight gradient) on 2x the tokens")
     args = ap.parse_args()
+    if args.backward:
+        return backward_case(2 * args.tokens, args.experts)
     big = torch.randn(32768, 2048, device="cuda").bfloat16()
     ops.quant_fp8_1x128(big)
     del big
