@@ -18,7 +18,9 @@ backward  home: dOut quantised once per token and permuted (FP8 codes + scales f
 
 Ordering between ranks: one all-gather of the padded segment offsets (host-read) in the forward,
 one-word all-reduces as fences before the owners read and after they have written.  fp32 block
-scales only.  Everything is issued on the current stream.
+scales only.  The copies run on two side streams: every peer's run is copied in while the own
+run computes, results are copied home beside the next GEMMs; the current stream waits for both
+side streams before each fence.
 """
 from __future__ import annotations
 
@@ -29,6 +31,13 @@ import torch.distributed as dist
 
 from . import ops
 from .ep import SegContext
+
+
+def _order(first: torch.cuda.Stream, then: torch.cuda.Stream) -> None:
+    """``then`` waits for everything queued on ``first`` so far."""
+    ev = torch.cuda.Event()
+    ev.record(first)
+    then.wait_event(ev)
 
 
 def _runs(everyone, me: int, world: int, El: int):
@@ -74,6 +83,27 @@ class _RoutedExpertsSeg(torch.autograd.Function):
         dist.all_gather_into_tensor(gathered, mine.contiguous(), group=seg.group)
         everyone = gathered.tolist()                 # the one host synchronisation
         runs = _runs(everyone, me, world, El)
+        main = torch.cuda.current_stream()
+        cin, cout = seg.side_streams()
+        _order(main, cin)
+        # every peer's run is copied in on a side stream now, while this rank's own run computes
+        arrivals = {}
+        with torch.cuda.stream(cin):
+            for g, r0, r1, Pg, po in runs:
+                n = r1 - r0
+                if g == me or n == 0:
+                    continue
+                ac = torch.empty((n, D), dtype=torch.uint8, device=dev)
+                asc = torch.empty((nkb, n), dtype=torch.float32, device=dev)
+                w = torch.empty(n, dtype=torch.float32, device=dev)
+                tiles = torch.empty(n // 128, dtype=torch.int32, device=dev)
+                seg.copy(ac.data_ptr(), n * D, seg.addr("codes", g) + r0 * D, n * D, n * D)
+                seg.copy(asc.data_ptr(), n * 4, seg.addr("scales", g) + r0 * 4, Pg * 4, n * 4, nkb)
+                seg.copy(w.data_ptr(), n * 4, seg.addr("weight", g) + r0 * 4, n * 4, n * 4)
+                seg.copy(tiles.data_ptr(), n // 32, seg.addr("tiles", g) + r0 // 32, n // 32, n // 32)
+                ev = torch.cuda.Event()
+                ev.record(cin)
+                arrivals[g] = (ac, asc, w, tiles, ev)
         saved = []
         for g, r0, r1, Pg, po in runs:
             n = r1 - r0
@@ -84,14 +114,8 @@ class _RoutedExpertsSeg(torch.autograd.Function):
                 ac, asc, w, tiles = codes[r0:r1], scales[:, r0:r1], w_rows[r0:r1], t_rows[r0 // 128:r1 // 128]
                 y = y_mine[r0:r1]
             else:
-                ac = torch.empty((n, D), dtype=torch.uint8, device=dev)
-                asc = torch.empty((nkb, n), dtype=torch.float32, device=dev)
-                w = torch.empty(n, dtype=torch.float32, device=dev)
-                tiles = torch.empty(n // 128, dtype=torch.int32, device=dev)
-                seg.copy(ac.data_ptr(), n * D, seg.addr("codes", g) + r0 * D, n * D, n * D)
-                seg.copy(asc.data_ptr(), n * 4, seg.addr("scales", g) + r0 * 4, Pg * 4, n * 4, nkb)
-                seg.copy(w.data_ptr(), n * 4, seg.addr("weight", g) + r0 * 4, n * 4, n * 4)
-                seg.copy(tiles.data_ptr(), n // 32, seg.addr("tiles", g) + r0 // 32, n // 32, n // 32)
+                ac, asc, w, tiles, ev = arrivals[g]
+                main.wait_event(ev)
                 y = None
             if need_grad and g == me:     # the buffers are rewritten before the backward runs
                 w, tiles = w.clone(), tiles.clone()
@@ -103,9 +127,13 @@ class _RoutedExpertsSeg(torch.autograd.Function):
                                                           wq.w13_scale, sub, limit,
                                                           save_gate_up=need_grad, save_h=need_grad)
             y = ops.gemm_fp8(ops.A_CONTIGUOUS, h_codes, h_scale, wq.w2_codes, wq.w2_scale, sub, out=y)
-            if g != me:
-                seg.copy(seg.addr("y", g) + r0 * D * 2, n * D * 2, y.data_ptr(), n * D * 2, n * D * 2)
+            if g != me:                               # results go home beside the next run's GEMMs
+                _order(main, cout)
+                with torch.cuda.stream(cout):
+                    seg.copy(seg.addr("y", g) + r0 * D * 2, n * D * 2, y.data_ptr(), n * D * 2, n * D * 2)
             saved.append((sub, gate, up, h, y))      # y kept alive until the fence below
+        _order(cin, main)
+        _order(cout, main)
         seg.fence()
         out = ops.combine(y_mine, lay.row_of_flat, T, k, shared)
         if need_grad:
@@ -141,6 +169,28 @@ class _RoutedExpertsSeg(torch.autograd.Function):
             ops.gather_rows(x, lay.row_token, out=x16)
         seg.fence()                                   # every rank's buffers hold this step's rows
         dw = [torch.zeros(s, dtype=torch.float32, device=dev) for s in wshapes] if need_w else None
+        main = torch.cuda.current_stream()
+        cin, cout = seg.side_streams()
+        _order(main, cin)
+        arrivals = {}
+        with torch.cuda.stream(cin):                  # peers' runs arrive while the own run computes
+            for g, r0, r1, Pg, _ in runs:
+                n = r1 - r0
+                if g == me or n == 0:
+                    continue
+                dyc = torch.empty((n, D), dtype=torch.uint8, device=dev)
+                dys = torch.empty((nkb, n), dtype=torch.float32, device=dev)
+                seg.copy(dyc.data_ptr(), n * D, seg.addr("codes", g) + r0 * D, n * D, n * D)
+                seg.copy(dys.data_ptr(), n * 4, seg.addr("scales", g) + r0 * 4, Pg * 4, n * 4, nkb)
+                dy_rows = x_rows = None
+                if need_w:
+                    dy_rows = torch.empty((n, D), dtype=torch.bfloat16, device=dev)
+                    x_rows = torch.empty((n, D), dtype=torch.bfloat16, device=dev)
+                    seg.copy(dy_rows.data_ptr(), n * D * 2, seg.addr("dy16", g) + r0 * D * 2, n * D * 2, n * D * 2)
+                    seg.copy(x_rows.data_ptr(), n * D * 2, seg.addr("x16", g) + r0 * D * 2, n * D * 2, n * D * 2)
+                ev = torch.cuda.Event()
+                ev.record(cin)
+                arrivals[g] = (dyc, dys, dy_rows, x_rows, ev)
         keep = []
         for (g, r0, r1, Pg, _), sv in zip(runs, saved):
             n = r1 - r0
@@ -151,15 +201,8 @@ class _RoutedExpertsSeg(torch.autograd.Function):
                 dyc, dys = codes[r0:r1], scales[:, r0:r1]
                 dy_rows, x_rows = dy16[r0:r1], x16[r0:r1]
             else:
-                dyc = torch.empty((n, D), dtype=torch.uint8, device=dev)
-                dys = torch.empty((nkb, n), dtype=torch.float32, device=dev)
-                seg.copy(dyc.data_ptr(), n * D, seg.addr("codes", g) + r0 * D, n * D, n * D)
-                seg.copy(dys.data_ptr(), n * 4, seg.addr("scales", g) + r0 * 4, Pg * 4, n * 4, nkb)
-                if need_w:
-                    dy_rows = torch.empty((n, D), dtype=torch.bfloat16, device=dev)
-                    x_rows = torch.empty((n, D), dtype=torch.bfloat16, device=dev)
-                    seg.copy(dy_rows.data_ptr(), n * D * 2, seg.addr("dy16", g) + r0 * D * 2, n * D * 2, n * D * 2)
-                    seg.copy(x_rows.data_ptr(), n * D * 2, seg.addr("x16", g) + r0 * D * 2, n * D * 2, n * D * 2)
+                dyc, dys, dy_rows, x_rows, ev = arrivals[g]
+                main.wait_event(ev)
             dact = ops.gemm_fp8(ops.A_CONTIGUOUS, dyc, dys, wq.w2_codes_t, wq.w2_scale, sub,
                                 b_scale_transposed=True)[:, :I]
             if not dact.is_contiguous():
@@ -169,13 +212,17 @@ class _RoutedExpertsSeg(torch.autograd.Function):
                                    wq.w13_scale, sub, b_scale_transposed=True)
             if dx_rows.shape[1] != D:
                 dx_rows = dx_rows[:, :D].contiguous()
-            seg.copy(seg.addr("dx", g) + r0 * D * 2, n * D * 2, dx_rows.data_ptr(), n * D * 2, n * D * 2)
-            seg.copy(seg.addr("dws", g) + r0 * 4, n * 4, dws_rows.data_ptr(), n * 4, n * 4)
+            _order(main, cout)
+            with torch.cuda.stream(cout):             # goes home beside this run's weight gradients
+                seg.copy(seg.addr("dx", g) + r0 * D * 2, n * D * 2, dx_rows.data_ptr(), n * D * 2, n * D * 2)
+                seg.copy(seg.addr("dws", g) + r0 * 4, n * 4, dws_rows.data_ptr(), n * 4, n * 4)
             keep.append((dx_rows, dws_rows))
             if need_w:
                 dw[2] += ops.wgrad_bf16(dy_rows.contiguous(), h, sub)          # [El, D, I]
                 dw[0] += ops.wgrad_bf16(dgate, x_rows.contiguous(), sub)       # [El, I, D]
                 dw[1] += ops.wgrad_bf16(dup, x_rows.contiguous(), sub)
+        _order(cin, main)
+        _order(cout, main)
         seg.fence()                                   # dx / dws rows of every owner have landed
         dx = ops.combine(bf("dx"), lay.row_of_flat, T, k)
         dws = own["dws"].view(torch.float32)[:P][lay.row_of_flat.long()].view(T, k)
