@@ -139,3 +139,15 @@ def test_plan_segments_slices_and_order():
     own, jobs = ep.plan_segments(B, 2, slice_rows=256)
     assert own == (384, 640, 896)
     assert jobs == [(0, 256, 256), (0, 512, 128)]                   # rank 1 has none for owner 2
+
+
+def test_training_runs_follow_the_gathered_offsets():
+    from nanov41_b200.ep_autograd import _runs
+    # 2 ranks, 4 experts (2 per rank); per rank: pad_off over all experts (5 entries) + P
+    everyone = [[0, 128, 128, 384, 512, 768], [0, 0, 256, 256, 640, 896]]
+    runs = _runs(everyone, 1, 2, 2)
+    # rank 1 owns experts 2..3: its own buffers first, then rank 0's
+    assert [(g, r0, r1, P) for g, r0, r1, P, _ in runs] == [(1, 256, 640, 896), (0, 128, 512, 768)]
+    assert runs[0][4] == [256, 256, 640] and runs[1][4] == [128, 384, 512]
+    runs0 = _runs(everyone, 0, 2, 2)
+    assert [(g, r0, r1) for g, r0, r1, _, _ in runs0] == [(0, 0, 128), (1, 0, 256)]
