@@ -275,6 +275,13 @@ int nv41_swiglu_bwd_quant(const void* dact, const void* gate, const void* up,
 int nv41_moe_wgrad_bf16(const void* a_rows, const void* b_rows, const int* pad_off, int E, int M,
                         int N, long long P_max, void* out, unsigned* status, void* stream);
 
+/* The same product added to an fp32 accumulator: acc[e] += A[rows_e]^T @ B[rows_e], acc fp32
+ * [E, M, N] (experts without rows are left untouched).  For gradients summed over several row
+ * sets (micro-batches; the runs of an expert-parallel owner) with a single rounding at the end,
+ * the accumulate-in-fp32 of nanov41/triton_grouped_moe.py:277-296 carried across launches. */
+int nv41_moe_wgrad_acc_f32(const void* a_rows, const void* b_rows, const int* pad_off, int E, int M,
+                           int N, long long P_max, float* acc, unsigned* status, void* stream);
+
 /* ---- expert parallelism over peer-mapped memory ---------------------------------------------
  * No reference counterpart: the reference shards experts only through replicated tokens and an
  * fp32 all_reduce of the layer output (nanov41/fast_moe.py:446-450,468-471;

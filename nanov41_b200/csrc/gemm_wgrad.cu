@@ -43,7 +43,8 @@ struct Args {
   CUtensorMap tmap_a;            // [P_max, M] bf16, box 64 x 64
   CUtensorMap tmap_b;            // [P_max, N] bf16, box 64 x 64
   const int* pad_off;            // [E + 1] padded segment offsets (multiples of 128)
-  __nv_bfloat16* out;            // [E, M, N]
+  __nv_bfloat16* out;            // [E, M, N] (bf16 store), or
+  float* acc;                    // [E, M, N] fp32, incremented (kAccumulate)
   int E, M, N, tiles_m, tiles_n;
   uint32_t* status;
 };
@@ -97,6 +98,7 @@ struct UnitIter {
   }
 };
 
+template <bool kAccumulate>
 __global__ void __launch_bounds__(kThreads, 1) wgrad_kernel(const __grid_constant__ Args g) {
   extern __shared__ uint8_t smem_raw[];
   Smem sm;
@@ -205,9 +207,11 @@ __global__ void __launch_bounds__(kThreads, 1) wgrad_kernel(const __grid_constan
       const Unit un = decode(g, order, u);
       const int m = un.mt * kTM + q * 32 + lane;
       const int n0 = un.nt * kTN + half * 128;
-      __nv_bfloat16* dst = g.out + (static_cast<long long>(un.e) * g.M + m) * g.N + n0;
+      const long long o = (static_cast<long long>(un.e) * g.M + m) * g.N + n0;
+      __nv_bfloat16* dst = g.out + o;
+      float* adst = g.acc + o;
       if (un.ksteps == 0) {
-        if (m < g.M) {
+        if (!kAccumulate && m < g.M) {       // nothing to add to an accumulator
           for (int i = 0; i < 128; i += 8)
             if (n0 + i < g.N) *reinterpret_cast<uint4*>(dst + i) = make_uint4(0u, 0u, 0u, 0u);
         }
@@ -225,17 +229,29 @@ __global__ void __launch_bounds__(kThreads, 1) wgrad_kernel(const __grid_constan
 #pragma unroll
           for (int i = 0; i < 16; i += 8) {
             if (n0 + c * 16 + i < g.N) {
-              uint4 o;
-              __nv_bfloat162 p;
-              p = __floats2bfloat162_rn(__uint_as_float(v[i]), __uint_as_float(v[i + 1]));
-              o.x = *reinterpret_cast<uint32_t*>(&p);
-              p = __floats2bfloat162_rn(__uint_as_float(v[i + 2]), __uint_as_float(v[i + 3]));
-              o.y = *reinterpret_cast<uint32_t*>(&p);
-              p = __floats2bfloat162_rn(__uint_as_float(v[i + 4]), __uint_as_float(v[i + 5]));
-              o.z = *reinterpret_cast<uint32_t*>(&p);
-              p = __floats2bfloat162_rn(__uint_as_float(v[i + 6]), __uint_as_float(v[i + 7]));
-              o.w = *reinterpret_cast<uint32_t*>(&p);
-              *reinterpret_cast<uint4*>(dst + c * 16 + i) = o;
+              if (kAccumulate) {
+                // this (expert, tile) belongs to one CTA of this launch: plain read-modify-write
+                float4* p4 = reinterpret_cast<float4*>(adst + c * 16 + i);
+                float4 lo = p4[0], hi = p4[1];
+                lo.x += __uint_as_float(v[i]);     lo.y += __uint_as_float(v[i + 1]);
+                lo.z += __uint_as_float(v[i + 2]); lo.w += __uint_as_float(v[i + 3]);
+                hi.x += __uint_as_float(v[i + 4]); hi.y += __uint_as_float(v[i + 5]);
+                hi.z += __uint_as_float(v[i + 6]); hi.w += __uint_as_float(v[i + 7]);
+                p4[0] = lo;
+                p4[1] = hi;
+              } else {
+                uint4 o4;
+                __nv_bfloat162 p;
+                p = __floats2bfloat162_rn(__uint_as_float(v[i]), __uint_as_float(v[i + 1]));
+                o4.x = *reinterpret_cast<uint32_t*>(&p);
+                p = __floats2bfloat162_rn(__uint_as_float(v[i + 2]), __uint_as_float(v[i + 3]));
+                o4.y = *reinterpret_cast<uint32_t*>(&p);
+                p = __floats2bfloat162_rn(__uint_as_float(v[i + 4]), __uint_as_float(v[i + 5]));
+                o4.z = *reinterpret_cast<uint32_t*>(&p);
+                p = __floats2bfloat162_rn(__uint_as_float(v[i + 6]), __uint_as_float(v[i + 7]));
+                o4.w = *reinterpret_cast<uint32_t*>(&p);
+                *reinterpret_cast<uint4*>(dst + c * 16 + i) = o4;
+              }
             }
           }
         }
@@ -262,9 +278,9 @@ __global__ void __launch_bounds__(kThreads, 1) wgrad_kernel(const __grid_constan
 
 using namespace nv41;
 
-extern "C" int nv41_moe_wgrad_bf16(const void* a_rows, const void* b_rows, const int* pad_off,
-                                   int E, int M, int N, long long P_max, void* out,
-                                   unsigned* status, void* stream) {
+static int launch_wgrad(bool accumulate, const void* a_rows, const void* b_rows, const int* pad_off,
+                        int E, int M, int N, long long P_max, void* out, unsigned* status,
+                        void* stream) {
   if (!a_rows || !b_rows || !pad_off || !out || !status || E <= 0 || M <= 0 || N <= 0 ||
       P_max <= 0 || (P_max % 128) != 0)
     return NV41_ERR_INVALID;
@@ -276,24 +292,37 @@ extern "C" int nv41_moe_wgrad_bf16(const void* a_rows, const void* b_rows, const
   rc = make_tmap_2d(&g.tmap_b, b_rows, static_cast<unsigned long long>(P_max), N, 2, 64, 64);
   if (rc != NV41_OK) return rc;
   g.pad_off = pad_off;
-  g.out = static_cast<__nv_bfloat16*>(out);
+  g.out = accumulate ? nullptr : static_cast<__nv_bfloat16*>(out);
+  g.acc = accumulate ? static_cast<float*>(out) : nullptr;
   g.E = E;
   g.M = M;
   g.N = N;
   g.tiles_m = (M + wgrad::kTM - 1) / wgrad::kTM;
   g.tiles_n = (N + wgrad::kTN - 1) / wgrad::kTN;
   g.status = status;
-  static bool configured = false;
-  if (!configured) {
-    if (cudaFuncSetAttribute(wgrad::wgrad_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+  auto* kern = accumulate ? wgrad::wgrad_kernel<true> : wgrad::wgrad_kernel<false>;
+  static bool configured[2] = {false, false};
+  if (!configured[accumulate]) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              wgrad::kSmemBytes) != cudaSuccess)
       return NV41_ERR_CUDA;
-    configured = true;
+    configured[accumulate] = true;
   }
   const long long units = static_cast<long long>(E) * g.tiles_m * g.tiles_n;
   int grid = persistent_grid(sm_count());
   if (units < grid) grid = static_cast<int>(units);
-  wgrad::wgrad_kernel<<<grid, wgrad::kThreads, wgrad::kSmemBytes,
-                        static_cast<cudaStream_t>(stream)>>>(g);
+  kern<<<grid, wgrad::kThreads, wgrad::kSmemBytes, static_cast<cudaStream_t>(stream)>>>(g);
   return launch_status();
+}
+
+extern "C" int nv41_moe_wgrad_bf16(const void* a_rows, const void* b_rows, const int* pad_off,
+                                   int E, int M, int N, long long P_max, void* out,
+                                   unsigned* status, void* stream) {
+  return launch_wgrad(false, a_rows, b_rows, pad_off, E, M, N, P_max, out, status, stream);
+}
+
+extern "C" int nv41_moe_wgrad_acc_f32(const void* a_rows, const void* b_rows, const int* pad_off,
+                                      int E, int M, int N, long long P_max, float* acc,
+                                      unsigned* status, void* stream) {
+  return launch_wgrad(true, a_rows, b_rows, pad_off, E, M, N, P_max, acc, status, stream);
 }

@@ -218,9 +218,9 @@ class _RoutedExpertsSeg(torch.autograd.Function):
                 seg.copy(seg.addr("dws", g) + r0 * 4, n * 4, dws_rows.data_ptr(), n * 4, n * 4)
             keep.append((dx_rows, dws_rows))
             if need_w:
-                dw[2] += ops.wgrad_bf16(dy_rows.contiguous(), h, sub)          # [El, D, I]
-                dw[0] += ops.wgrad_bf16(dgate, x_rows.contiguous(), sub)       # [El, I, D]
-                dw[1] += ops.wgrad_bf16(dup, x_rows.contiguous(), sub)
+                ops.wgrad_accumulate(dy_rows.contiguous(), h, sub, dw[2])      # [El, D, I]
+                ops.wgrad_accumulate(dgate, x_rows.contiguous(), sub, dw[0])   # [El, I, D]
+                ops.wgrad_accumulate(dup, x_rows.contiguous(), sub, dw[1])
         _order(cin, main)
         _order(cout, main)
         seg.fence()                                   # dx / dws rows of every owner have landed

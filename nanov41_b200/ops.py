@@ -462,6 +462,23 @@ def wgrad_bf16(a_rows: torch.Tensor, b_rows: torch.Tensor, layout: DeviceLayout)
     return out
 
 
+def wgrad_accumulate(a_rows: torch.Tensor, b_rows: torch.Tensor, layout: DeviceLayout,
+                     acc: torch.Tensor) -> torch.Tensor:
+    """acc[e] += a_rows[rows of e]^T @ b_rows[rows of e]; acc fp32 [E, M, N], contiguous."""
+    _need_cuda(a_rows, b_rows, acc)
+    P, M = a_rows.shape
+    N = b_rows.shape[1]
+    if not (a_rows.is_contiguous() and b_rows.is_contiguous()) or b_rows.shape[0] != P:
+        raise Nv41Error("wgrad_accumulate expects contiguous [P_max, *] bf16 operands")
+    if acc.dtype != torch.float32 or tuple(acc.shape) != (layout.E, M, N) or not acc.is_contiguous():
+        raise Nv41Error("wgrad_accumulate: acc must be contiguous fp32 [E, M, N]")
+    st = status_word(a_rows.device)
+    check(_lib.load().nv41_moe_wgrad_acc_f32(_ptr(a_rows), _ptr(b_rows), _ptr(layout.pad_off),
+                                             layout.E, M, N, P, _ptr(acc), _ptr(st), _stream()),
+          "nv41_moe_wgrad_acc_f32")
+    return acc
+
+
 def fp8_gate_up(x, wq: Fp8ExpertWeights, layout: DeviceLayout, limit: float, save: bool = False,
                 gather_in_gemm: bool = False):
     """Activation quantisation + gate/up GEMM + SwiGLU + re-quantised h, in either scale mode.

@@ -72,3 +72,12 @@ def test_wgrad_kernel_exact_on_small_integers():
     for e in range(E):
         ref = a[po[e]:po[e + 1]].float().t() @ b[po[e]:po[e + 1]].float()
         assert torch.equal(out[e].float(), ref.bfloat16().float()), e
+    # accumulating form: two launches into an fp32 buffer give exactly twice the integer product,
+    # and an expert without rows leaves its accumulator untouched
+    acc = torch.full((E, M, N), 3.0, device="cuda")
+    ops.wgrad_accumulate(a.cuda(), b.cuda(), lay, acc)
+    ops.wgrad_accumulate(a.cuda(), b.cuda(), lay, acc)
+    ops.check_status()
+    for e in range(E):
+        ref = a[po[e]:po[e + 1]].float().t() @ b[po[e]:po[e + 1]].float()
+        assert torch.equal(acc[e].cpu(), 2.0 * ref + 3.0), e
