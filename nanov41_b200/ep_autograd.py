@@ -17,8 +17,8 @@ backward  home: dOut quantised once per token and permuted (FP8 codes + scales f
           home: fp32 slot sum of the dX rows, dws read back per (token, slot).
 
 Ordering between ranks: one all-gather of the padded segment offsets (host-read) in the forward,
-one-word all-reduces as fences before the owners read and after they have written.  fp32 block
-scales only.  The copies run on two side streams: every peer's run is copied in while the own
+one-word all-reduces as fences before the owners read and after they have written.  fp32 or
+ue8m0 block scales (the e8m0 scale atoms travel with the codes).  The copies run on two side streams: every peer's run is copied in while the own
 run computes, results are copied home beside the next GEMMs; the current stream waits for both
 side streams before each fence.
 """
@@ -54,8 +54,9 @@ def _runs(everyone, me: int, world: int, El: int):
 class _RoutedExpertsSeg(torch.autograd.Function):
     @staticmethod
     def forward(actx, x, ws, shared, w1, w3, w2, indices, limit, wq, seg: SegContext, n_experts):
-        if wq.ue8m0:
-            raise ops.Nv41Error("expert-parallel training path: fp32 block scales only")
+        if wq.ue8m0 != seg.ue8m0:
+            raise ops.Nv41Error("SegContext and weights disagree on the scale format")
+        ue = wq.ue8m0
         world, me, dev = seg.world, seg.rank, seg.dev
         T, D = x.shape
         k = indices.shape[1]
@@ -71,8 +72,13 @@ class _RoutedExpertsSeg(torch.autograd.Function):
         codes = own["codes"][:P * D].view(P, D)
         scales = own["scales"].view(torch.float32)[:nkb * P].view(nkb, P)
         y_mine = own["y"].view(torch.bfloat16)[:P * D].view(P, D)
-        xc, xs = ops.quant_fp8_1x128(x, scale_kmajor=True)
-        ops.gather_fp8_rows(xc, xs, lay, False, out=(codes, scales, None))
+        abytes = nkb * 512                            # e8m0 scale atoms per 128-row tile (ue8m0)
+        atoms = None
+        if ue:
+            atoms = own["atoms"][:P // 128 * abytes]
+            atoms.zero_()
+        xc, xs = ops.quant_fp8_1x128(x, scale_kmajor=True, ue8m0=ue)
+        ops.gather_fp8_rows(xc, xs, lay, ue, out=(codes, scales, atoms))
         w_rows = own["weight"].view(torch.float32)[:P]
         w_rows.copy_(lay.row_weight)
         t_rows = own["tiles"].view(torch.int32)[:P // 128]
@@ -101,9 +107,14 @@ class _RoutedExpertsSeg(torch.autograd.Function):
                 seg.copy(asc.data_ptr(), n * 4, seg.addr("scales", g) + r0 * 4, Pg * 4, n * 4, nkb)
                 seg.copy(w.data_ptr(), n * 4, seg.addr("weight", g) + r0 * 4, n * 4, n * 4)
                 seg.copy(tiles.data_ptr(), n // 32, seg.addr("tiles", g) + r0 // 32, n // 32, n // 32)
+                sf = None
+                if ue:
+                    sf = torch.empty(n // 128 * abytes, dtype=torch.uint8, device=dev)
+                    seg.copy(sf.data_ptr(), sf.numel(), seg.addr("atoms", g) + r0 // 128 * abytes,
+                             sf.numel(), sf.numel())
                 ev = torch.cuda.Event()
                 ev.record(cin)
-                arrivals[g] = (ac, asc, w, tiles, ev)
+                arrivals[g] = (ac, asc, w, tiles, sf, ev)
         saved = []
         for g, r0, r1, Pg, po in runs:
             n = r1 - r0
@@ -112,9 +123,10 @@ class _RoutedExpertsSeg(torch.autograd.Function):
                 continue
             if g == me:
                 ac, asc, w, tiles = codes[r0:r1], scales[:, r0:r1], w_rows[r0:r1], t_rows[r0 // 128:r1 // 128]
+                sf = atoms[r0 // 128 * abytes:r1 // 128 * abytes] if ue else None
                 y = y_mine[r0:r1]
             else:
-                ac, asc, w, tiles, ev = arrivals[g]
+                ac, asc, w, tiles, sf, ev = arrivals[g]
                 main.wait_event(ev)
                 y = None
             if need_grad and g == me:     # the buffers are rewritten before the backward runs
@@ -123,10 +135,17 @@ class _RoutedExpertsSeg(torch.autograd.Function):
             meta = torch.tensor([n // 128, n, n, El], dtype=torch.int32, device=dev)
             sub = replace(lay, E=El, P_max=n, tile_expert=tiles, row_weight=w, row_token=seg.dummy,
                           flat_of_row=seg.dummy, pad_off=pad_off, meta=meta)
-            h_codes, h_scale, gate, up, h = ops.gemm1_fp8(ops.A_CONTIGUOUS, ac, asc, wq.w13_codes,
-                                                          wq.w13_scale, sub, limit,
-                                                          save_gate_up=need_grad, save_h=need_grad)
-            y = ops.gemm_fp8(ops.A_CONTIGUOUS, h_codes, h_scale, wq.w2_codes, wq.w2_scale, sub, out=y)
+            if ue:
+                h_codes, _, h_sf, gate, up, h = ops.gemm1_mx(ops.A_CONTIGUOUS, ac, None, sf,
+                                                             wq.w13_codes, wq.w13_sf, sub, limit,
+                                                             save_gate_up=need_grad, save_h=need_grad)
+                y = ops.gemm_mx(ops.A_CONTIGUOUS, h_codes, None, h_sf, wq.w2_codes, wq.w2_sf, sub, out=y)
+            else:
+                h_codes, h_scale, gate, up, h = ops.gemm1_fp8(ops.A_CONTIGUOUS, ac, asc, wq.w13_codes,
+                                                              wq.w13_scale, sub, limit,
+                                                              save_gate_up=need_grad, save_h=need_grad)
+                y = ops.gemm_fp8(ops.A_CONTIGUOUS, h_codes, h_scale, wq.w2_codes, wq.w2_scale, sub,
+                                 out=y)
             if g != me:                               # results go home beside the next run's GEMMs
                 _order(main, cout)
                 with torch.cuda.stream(cout):
@@ -160,8 +179,14 @@ class _RoutedExpertsSeg(torch.autograd.Function):
         dout = dout.to(torch.bfloat16).contiguous()
         codes = own["codes"][:P * D].view(P, D)
         scales = own["scales"].view(torch.float32)[:nkb * P].view(nkb, P)
-        dqc, dqs = ops.quant_fp8_1x128(dout, scale_kmajor=True)
-        ops.gather_fp8_rows(dqc, dqs, lay, False, out=(codes, scales, None))
+        ue = wq.ue8m0
+        abytes = nkb * 512
+        atoms = None
+        if ue:
+            atoms = own["atoms"][:P // 128 * abytes]
+            atoms.zero_()
+        dqc, dqs = ops.quant_fp8_1x128(dout, scale_kmajor=True, ue8m0=ue)
+        ops.gather_fp8_rows(dqc, dqs, lay, ue, out=(codes, scales, atoms))
         need_w = any(actx.needs_input_grad[3:6])
         dy16, x16 = bf("dy16"), bf("x16")
         if need_w:
@@ -182,7 +207,11 @@ class _RoutedExpertsSeg(torch.autograd.Function):
                 dys = torch.empty((nkb, n), dtype=torch.float32, device=dev)
                 seg.copy(dyc.data_ptr(), n * D, seg.addr("codes", g) + r0 * D, n * D, n * D)
                 seg.copy(dys.data_ptr(), n * 4, seg.addr("scales", g) + r0 * 4, Pg * 4, n * 4, nkb)
-                dy_rows = x_rows = None
+                dy_rows = x_rows = dsf = None
+                if ue:
+                    dsf = torch.empty(n // 128 * abytes, dtype=torch.uint8, device=dev)
+                    seg.copy(dsf.data_ptr(), dsf.numel(), seg.addr("atoms", g) + r0 // 128 * abytes,
+                             dsf.numel(), dsf.numel())
                 if need_w:
                     dy_rows = torch.empty((n, D), dtype=torch.bfloat16, device=dev)
                     x_rows = torch.empty((n, D), dtype=torch.bfloat16, device=dev)
@@ -190,7 +219,7 @@ class _RoutedExpertsSeg(torch.autograd.Function):
                     seg.copy(x_rows.data_ptr(), n * D * 2, seg.addr("x16", g) + r0 * D * 2, n * D * 2, n * D * 2)
                 ev = torch.cuda.Event()
                 ev.record(cin)
-                arrivals[g] = (dyc, dys, dy_rows, x_rows, ev)
+                arrivals[g] = (dyc, dys, dsf, dy_rows, x_rows, ev)
         keep = []
         for (g, r0, r1, Pg, _), sv in zip(runs, saved):
             n = r1 - r0
@@ -199,17 +228,27 @@ class _RoutedExpertsSeg(torch.autograd.Function):
             sub, gate, up, h = sv
             if g == me:
                 dyc, dys = codes[r0:r1], scales[:, r0:r1]
+                dsf = atoms[r0 // 128 * abytes:r1 // 128 * abytes] if ue else None
                 dy_rows, x_rows = dy16[r0:r1], x16[r0:r1]
             else:
-                dyc, dys, dy_rows, x_rows, ev = arrivals[g]
+                dyc, dys, dsf, dy_rows, x_rows, ev = arrivals[g]
                 main.wait_event(ev)
-            dact = ops.gemm_fp8(ops.A_CONTIGUOUS, dyc, dys, wq.w2_codes_t, wq.w2_scale, sub,
-                                b_scale_transposed=True)[:, :I]
+            if ue:
+                dact = ops.gemm_mx(ops.A_CONTIGUOUS, dyc, None, dsf, wq.w2_codes_t, wq.w2_sf_t,
+                                   sub)[:, :I]
+            else:
+                dact = ops.gemm_fp8(ops.A_CONTIGUOUS, dyc, dys, wq.w2_codes_t, wq.w2_scale, sub,
+                                    b_scale_transposed=True)[:, :I]
             if not dact.is_contiguous():
                 dact = dact.contiguous()
-            dgate, dup, dgu_codes, dgu_scale, dws_rows = ops.swiglu_bwd_quant(dact, gate, up, sub, limit)
-            dx_rows = ops.gemm_fp8(ops.A_CONTIGUOUS, dgu_codes, dgu_scale, wq.w13_codes_t,
-                                   wq.w13_scale, sub, b_scale_transposed=True)
+            dgate, dup, dgu_codes, dgu_scale, dws_rows = ops.swiglu_bwd_quant(dact, gate, up, sub,
+                                                                              limit, ue)
+            if ue:
+                dx_rows = ops.gemm_mx(ops.A_CONTIGUOUS, dgu_codes, None, ops.pack_sf_rows(dgu_scale),
+                                      wq.w13_codes_t, wq.w13_sf_t, sub)
+            else:
+                dx_rows = ops.gemm_fp8(ops.A_CONTIGUOUS, dgu_codes, dgu_scale, wq.w13_codes_t,
+                                       wq.w13_scale, sub, b_scale_transposed=True)
             if dx_rows.shape[1] != D:
                 dx_rows = dx_rows[:, :D].contiguous()
             _order(main, cout)
@@ -234,12 +273,14 @@ class _RoutedExpertsSeg(torch.autograd.Function):
 
 
 def experts_forward_ep(seg: SegContext, x, ws, indices, w1_local, w3_local, w2_local, n_experts: int,
-                       limit: float, shared=None, wq_local=None):
+                       limit: float, shared=None, wq_local=None, scale_fmt=None):
     """Differentiable expert-parallel routed experts.  x [T_local, D] bf16; ws / indices
     [T_local, k] (global expert ids); w*_local: this rank's experts ([E/G, I, D], [E/G, I, D],
     [E/G, D, I] bf16).  Gradients: x, ws, shared, and the local weights (summed over the rows of
-    all ranks).  ``wq_local``: pre-quantised local weights with transposed copies (optional)."""
+    all ranks).  ``wq_local``: pre-quantised local weights with transposed copies (optional);
+    ``scale_fmt``: None (fp32 block scales) or "ue8m0", matching the SegContext."""
     if wq_local is None:
-        wq_local = ops.quantize_expert_weights(w1_local, w3_local, w2_local, transposed=True)
+        wq_local = ops.quantize_expert_weights(w1_local, w3_local, w2_local, transposed=True,
+                                               ue8m0=scale_fmt == "ue8m0")
     return _RoutedExpertsSeg.apply(x, ws, shared, w1_local, w3_local, w2_local, indices,
                                    float(limit or 0.0), wq_local, seg, n_experts)

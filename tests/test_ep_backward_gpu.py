@@ -40,36 +40,38 @@ def _worker(rank, world, port):
         dout_all = torch.randn(CASE["T"], D, generator=gen, device="cuda").bfloat16()
         shared_all = torch.randn(CASE["T"], D, generator=gen, device="cuda").bfloat16()
 
-        # single GPU, all tokens, all experts: the reference for every gradient
-        xa = g["x"].clone().requires_grad_(True)
-        wsa = g["weights"].clone().requires_grad_(True)
-        sha = shared_all.clone().requires_grad_(True)
-        w1a, w3a, w2a = (g[n].clone().requires_grad_(True) for n in ("w1", "w3", "w2"))
-        out_a = autograd_moe.experts_forward(xa, wsa, g["indices"], w1a, w3a, w2a, 10.0, sha,
-                                             scale_fmt=None)
-        out_a.backward(dout_all)
+        for fmt in (None, "ue8m0"):
+            # single GPU, all tokens, all experts: the reference for every gradient
+            xa = g["x"].clone().requires_grad_(True)
+            wsa = g["weights"].clone().requires_grad_(True)
+            sha = shared_all.clone().requires_grad_(True)
+            w1a, w3a, w2a = (g[n].clone().requires_grad_(True) for n in ("w1", "w3", "w2"))
+            out_a = autograd_moe.experts_forward(xa, wsa, g["indices"], w1a, w3a, w2a, 10.0, sha,
+                                                 scale_fmt=fmt)
+            out_a.backward(dout_all)
 
-        seg = ep.SegContext(T, k, E, D, backward=True)
-        x = g["x"][sl].clone().requires_grad_(True)
-        ws = g["weights"][sl].clone().requires_grad_(True)
-        sh = shared_all[sl].clone().requires_grad_(True)
-        w1, w3, w2 = (g[n][rank * El:(rank + 1) * El].clone().requires_grad_(True)
-                      for n in ("w1", "w3", "w2"))
-        for step in range(2):                       # twice through the same buffers
-            for t in (x, ws, sh, w1, w3, w2):
-                t.grad = None
-            out = ep_autograd.experts_forward_ep(seg, x, ws, g["indices"][sl], w1, w3, w2, E, 10.0, sh)
-            out.backward(dout_all[sl])
-            ops.check_status()
-            assert torch.equal(out, out_a[sl]), step
-            assert torch.equal(x.grad, xa.grad[sl]), step
-            assert torch.equal(ws.grad, wsa.grad[sl]), step
-            assert torch.equal(sh.grad, sha.grad[sl]), step
-            for got, want, name in ((w1.grad, w1a.grad, "dw1"), (w3.grad, w3a.grad, "dw3"),
-                                    (w2.grad, w2a.grad, "dw2")):
-                mx, mean = OM.rel_errors(got.cpu(), want[rank * El:(rank + 1) * El].cpu().float())
-                assert mx <= 2e-2 and mean <= 2e-3, (name, mx, mean)
-        seg.close()
+            seg = ep.SegContext(T, k, E, D, ue8m0=fmt == "ue8m0", backward=True)
+            x = g["x"][sl].clone().requires_grad_(True)
+            ws = g["weights"][sl].clone().requires_grad_(True)
+            sh = shared_all[sl].clone().requires_grad_(True)
+            w1, w3, w2 = (g[n][rank * El:(rank + 1) * El].clone().requires_grad_(True)
+                          for n in ("w1", "w3", "w2"))
+            for step in range(2):                       # twice through the same buffers
+                for t in (x, ws, sh, w1, w3, w2):
+                    t.grad = None
+                out = ep_autograd.experts_forward_ep(seg, x, ws, g["indices"][sl], w1, w3, w2, E,
+                                                     10.0, sh, scale_fmt=fmt)
+                out.backward(dout_all[sl])
+                ops.check_status()
+                assert torch.equal(out, out_a[sl]), step
+                assert torch.equal(x.grad, xa.grad[sl]), step
+                assert torch.equal(ws.grad, wsa.grad[sl]), step
+                assert torch.equal(sh.grad, sha.grad[sl]), step
+                for got, want, name in ((w1.grad, w1a.grad, "dw1"), (w3.grad, w3a.grad, "dw3"),
+                                        (w2.grad, w2a.grad, "dw2")):
+                    mx, mean = OM.rel_errors(got.cpu(), want[rank * El:(rank + 1) * El].cpu().float())
+                    assert mx <= 2e-2 and mean <= 2e-3, (name, mx, mean)
+            seg.close()
         dist.barrier()
     finally:
         dist.destroy_process_group()
