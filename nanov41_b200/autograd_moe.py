@@ -123,6 +123,43 @@ def stacked_weights(experts):
     return w1, w3, w2
 
 
+def routed_experts_sharded(moe, xf, weights, indices):
+    """This rank's share of the routed experts when the experts of ``moe`` are sharded over ranks
+    that all hold the SAME tokens (nanov41/fast_moe.py:419-450 on a sharded rank, official
+    scheme nanov41/_ref_patched_model.py:880-887): fp32 [T, dim] with the rows of the other
+    ranks' experts contributing zero, to be summed by the caller's all_reduce.  The layout is
+    built over all experts; only the tiles of the local experts are computed.  Inference only."""
+    from dataclasses import replace
+    if torch.is_grad_enabled() and (xf.requires_grad or weights.requires_grad):
+        raise ops.Nv41Error("sharded experts with replicated tokens: forward only "
+                            "(training goes through nanov41_b200.ep_autograd)")
+    experts = _expert_list(moe)
+    limit = getattr(experts[0], "swiglu_limit", 0.0) or 0.0
+    start, n_local = moe.experts_start_idx, len(experts)
+    key = _weights_key(experts)
+    cached = getattr(moe, _WQ_ATTR, None)
+    ue8m0 = SCALE_FMT == "ue8m0"
+    if cached is None or cached[0] != key or cached[1].ue8m0 != ue8m0:
+        with torch.no_grad():
+            w1, w3, w2 = stacked_weights(experts)
+            cached = (key, ops.quantize_expert_weights(w1, w3, w2, ue8m0=ue8m0))
+        setattr(moe, _WQ_ATTR, cached)
+    wq = cached[1]
+    T, D = xf.shape
+    k = indices.shape[1]
+    lay = ops.build_layout(indices.reshape(-1), moe.n_routed_experts, k, weights.reshape(-1))
+    te = lay.tile_expert
+    local = (te >= start) & (te < start + n_local)
+    sub = replace(lay, E=n_local, tile_expert=torch.where(local, te - start, torch.full_like(te, -1)))
+    h_codes, h_scale, h_sf, _, _, _, _, _ = ops.fp8_gate_up(xf.contiguous(), wq, sub, limit)
+    y_rows = torch.zeros((lay.P_max, D), dtype=torch.bfloat16, device=xf.device)   # skipped tiles = 0
+    if wq.ue8m0:
+        ops.gemm_mx(ops.A_CONTIGUOUS, h_codes, None, h_sf, wq.w2_codes, wq.w2_sf, sub, out=y_rows)
+    else:
+        ops.gemm_fp8(ops.A_CONTIGUOUS, h_codes, h_scale, wq.w2_codes, wq.w2_scale, sub, out=y_rows)
+    return ops.combine(y_rows, lay.row_of_flat, T, k, out_fp32=True)
+
+
 def routed_experts(moe, xf, weights, indices, shared):
     """Routed experts of an ``MoE`` module (the ``self`` contract of
     nanov41/_ref_patched_model.py:875-904).  Under no_grad (or with frozen weights) the
