@@ -349,13 +349,15 @@ def run_ep(args, world, rank, local, dev):
                            ep_copy_sms=args.ep_copy_sms), "scale_fmt": args.scale_fmt,
             "e2e": {"value": flops / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s",
                     "ms_per_step": ms_e2e,
-                    "h2d_bytes_per_step": x_host.numel() * 2 + idx_host.numel() * 8 + w_host.numel() * 4,
-                    "d2h_bytes_per_step": out_host.numel() * 2,
+                    # whole job: every rank moves its own tokens in and its results out
+                    "h2d_bytes_per_step": world * (x_host.numel() * 2 + idx_host.numel() * 8
+                                                   + w_host.numel() * 4),
+                    "d2h_bytes_per_step": world * out_host.numel() * 2,
                     "pipeline": "double-buffered: copies of steps i+1 / i-1 on side streams"},
             # per rank and step: layout x3, quantiser, row permute, combine + one GEMM pair for
             # each half of the own run and for each peer's slice (one slice per peer at this size)
             "gpu_launches": world * args.steps * (6 + 2 * (2 + (world - 1))), "clocks": clocks,
-            "roofline": {"bound": "tensor", "kernel": "whole EP step (GEMMs + all-to-all)",
+            "roofline": {"bound": "tensor", "kernel": "whole EP step (GEMMs + copies over NVLink)",
                          "achieved": tfl / world, "peak": 2.0 * bf16_peak, "unit": "TFLOP/s",
                          "frac": tfl / world / (2.0 * bf16_peak), "traffic": None,
                          "peak_note": "per-GPU share of the step vs 2 x measured bf16 burst"},
