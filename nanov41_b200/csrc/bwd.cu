@@ -178,7 +178,7 @@ swiglu_bwd_quant_kernel(const __nv_bfloat16* __restrict__ dact, const __nv_bfloa
     for (int c0 = 0; c0 < I; c0 += 256) {
       const int col = c0 + lane * 8;
       const bool in = col < I;
-      float d[8], g[8], u[8], dg[8], du[8];
+      float d[8], g[8], u[8];
 #pragma unroll
       for (int i = 0; i < 8; ++i) d[i] = g[i] = u[i] = 0.f;
       if (in) {

@@ -295,7 +295,7 @@ __device__ __forceinline__ void role_promote(const GemmArgs& g, const SM& sm, ui
       if (!mbar_wait<40>(sm.tfull(b), tph, sm.abort_flag(), g.status, ST_TIMEOUT_TMEM_FULL)) return;
       tc_fence_after_sync();
       const uint32_t tb = lane_base + b * kBN;
-      if (EPI == EPI_STORE) {
+      if constexpr (EPI == EPI_STORE) {
         // plain tiles have no SwiGLU warps, so these warps own more registers: 64-column pieces,
         // two TMEM round trips per K block
         uint32_t wa[64];
@@ -312,25 +312,25 @@ __device__ __forceinline__ void role_promote(const GemmArgs& g, const SM& sm, ui
           for (int i = 0; i < 64; ++i)
             acc[c * 64 + i] = fmaf(__uint_as_float(wa[i]), f0, acc[c * 64 + i]);
         }
-        continue;
-      }
-      // gate|up tiles: 32-column pieces (gate half*64 + {0,32}, then up 128 + half*64 + {0,32});
-      // fewer, larger TMEM reads cost less than many small overlapped ones
-      uint32_t va[32];
+      } else {
+        // gate|up tiles: 32-column pieces (gate half*64 + {0,32}, then up 128 + half*64 +
+        // {0,32}); fewer, larger TMEM reads cost less than many small overlapped ones
+        uint32_t va[32];
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        const float fa = (c >= 2) ? f1 : f0;
-        tmem_ld_32x32b_x32(tb + (c >> 1) * 128 + half * 64 + (c & 1) * 32, va);
-        tmem_ld_wait_x32(va);
-        if (c == 3) {
-          // every piece of this buffer is in registers: hand it back to the UMMA warp
-          tc_fence_before_sync();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(sm.tempty(b));
+        for (int c = 0; c < 4; ++c) {
+          const float fa = (c >= 2) ? f1 : f0;
+          tmem_ld_32x32b_x32(tb + (c >> 1) * 128 + half * 64 + (c & 1) * 32, va);
+          tmem_ld_wait_x32(va);
+          if (c == 3) {
+            // every piece of this buffer is in registers: hand it back to the UMMA warp
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(sm.tempty(b));
+          }
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            acc[c * 32 + i] = fmaf(__uint_as_float(va[i]), fa, acc[c * 32 + i]);
         }
-#pragma unroll
-        for (int i = 0; i < 32; ++i)
-          acc[c * 32 + i] = fmaf(__uint_as_float(va[i]), fa, acc[c * 32 + i]);
       }
     }
 

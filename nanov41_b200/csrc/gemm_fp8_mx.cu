@@ -30,6 +30,9 @@
 #include "tmap.cuh"
 #include "util.cuh"
 
+// the unit-iteration macro declares (mt, nt, e) for every role; some roles use only one of them
+#pragma nv_diag_suppress 550
+
 namespace nv41 {
 namespace mx {
 
