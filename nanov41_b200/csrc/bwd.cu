@@ -149,9 +149,8 @@ __device__ __forceinline__ uint2 quant_bf16x8(const uint4& v, uint32_t amax_bits
 #pragma unroll
     for (int o = 8; o >= 1; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(hmask, amax, o));
     s = block_scale(amax, ue8m0);
-    const float r = __frcp_rn(s);
-    return make_uint2(e4m3x4_div(f[0], f[1], f[2], f[3], s, r),
-                      e4m3x4_div(f[4], f[5], f[6], f[7], s, r));
+    return make_uint2(e4m3x4_div(f[0], f[1], f[2], f[3], s),
+                      e4m3x4_div(f[4], f[5], f[6], f[7], s));
   }
   s = block_scale(__uint_as_float(amax_bits << 16), ue8m0);
   const float r = __frcp_rn(s);

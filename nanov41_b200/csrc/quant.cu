@@ -62,11 +62,10 @@ __device__ __forceinline__ void quant_1x128_chunk(const Chunk16& c, unsigned qma
 #pragma unroll
     for (int o = 4; o >= 1; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(qmask, amax, o));
     s = block_scale(amax, kUe8m0);
-    const float r = __frcp_rn(s);
-    lo.x = e4m3x4_div(f[0], f[1], f[2], f[3], s, r);
-    lo.y = e4m3x4_div(f[4], f[5], f[6], f[7], s, r);
-    hi.x = e4m3x4_div(g[0], g[1], g[2], g[3], s, r);
-    hi.y = e4m3x4_div(g[4], g[5], g[6], g[7], s, r);
+    lo.x = e4m3x4_div(f[0], f[1], f[2], f[3], s);
+    lo.y = e4m3x4_div(f[4], f[5], f[6], f[7], s);
+    hi.x = e4m3x4_div(g[0], g[1], g[2], g[3], s);
+    hi.y = e4m3x4_div(g[4], g[5], g[6], g[7], s);
   } else {
     s = block_scale(__uint_as_float(m << 16), kUe8m0);
     const float r = __frcp_rn(s);
@@ -197,8 +196,8 @@ quant_fp8_128x128_kernel(const __nv_bfloat16* __restrict__ w, int E, int N, int 
     } else {
       float f[8];
       unpack_bf16x8(v[p], f);
-      out.x = e4m3x4_div(f[0], f[1], f[2], f[3], s, rcp);
-      out.y = e4m3x4_div(f[4], f[5], f[6], f[7], s, rcp);
+      out.x = e4m3x4_div(f[0], f[1], f[2], f[3], s);
+      out.y = e4m3x4_div(f[4], f[5], f[6], f[7], s);
     }
     if (r < N) {
       *reinterpret_cast<uint2*>(codes + (static_cast<long long>(e) * N + r) * Kpad + col) = out;

@@ -31,37 +31,30 @@ __device__ __forceinline__ float block_scale(float amax, int ue8m0) {
   return s;
 }
 
-// Correctly rounded a / s given r = RN(1 / s): a product and two FMA correction steps.  Exact for
-// the quantizers' operand range (s a normal number >= 1e-4/448 scale, |a / s| <= 448 (1 + eps));
-// checked against IEEE division on 4e8 (bf16 a, fp32 s) pairs.  Non-finite or huge |a| take the
-// IEEE division; -0.0 keeps its sign (the FMA chain alone would lose it).
-__device__ __forceinline__ float div_by_scale(float a, float s, float r) {
-  if (!(fabsf(a) <= 1.0e30f)) return __fdiv_rn(a, s);
-  float q = a * r;
-  float e = fmaf(-s, q, a);
-  q = fmaf(e, r, q);
-  e = fmaf(-s, q, a);
-  return copysignf(fmaf(e, r, q), a);
-}
-
-// e4m3 codes (RN-even, saturating) of clamp(x / s, +-448) for four values
-__device__ __forceinline__ uint32_t e4m3x4_div(float a, float b, float c, float d, float s,
-                                               float r) {
-  const float q0 = fminf(fmaxf(div_by_scale(a, s, r), -448.f), 448.f);
-  const float q1 = fminf(fmaxf(div_by_scale(b, s, r), -448.f), 448.f);
-  const float q2 = fminf(fmaxf(div_by_scale(c, s, r), -448.f), 448.f);
-  const float q3 = fminf(fmaxf(div_by_scale(d, s, r), -448.f), 448.f);
+// e4m3 codes (RN-even, saturating) of clamp(x / s, +-448) for four values by IEEE division: the
+// path of blocks that hold an inf or a NaN (the packed division below needs finite operands).
+// With s = inf the finite values give +-0 and inf / inf = NaN clamps to -448, the behaviour of
+// min(max(., -448), 448) with CUDA's NaN-dropping min / max as in ref/kernel.py:84-88.
+__device__ __forceinline__ uint32_t e4m3x4_div(float a, float b, float c, float d, float s) {
+  const float q0 = fminf(fmaxf(__fdiv_rn(a, s), -448.f), 448.f);
+  const float q1 = fminf(fmaxf(__fdiv_rn(b, s), -448.f), 448.f);
+  const float q2 = fminf(fmaxf(__fdiv_rn(c, s), -448.f), 448.f);
+  const float q3 = fminf(fmaxf(__fdiv_rn(d, s), -448.f), 448.f);
   const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(q0, q1), __NV_SATFINITE, __NV_E4M3);
   const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(q2, q3), __NV_SATFINITE, __NV_E4M3);
   return lo | (hi << 16);
 }
 
-// ---- packed (two floats per instruction) form of the same division, for finite operands
+// ---- packed (two floats per instruction) division for finite operands: q = a * r with
+// r = RN(1 / s), then two FMA correction steps e = a - s q, q += e r.  Correctly rounded for the
+// quantizers' operand range (s a normal number >= 1e-4 / 448, |a / s| <= 448 (1 + eps)); checked
+// against IEEE division on 4e8 (bf16 a, fp32 s) pairs.
+//
 // e4m3 codes of eight FINITE values given as four words of two bf16 each (element 2i in the low
-// half), divided by the block scale s (ns2 = {-s, -s}, r2 = {RN(1/s), RN(1/s)}).  Same
-// arithmetic as div_by_scale per lane: |x / s| <= 448 (1 + eps) by construction of s, so the
-// saturating conversion needs no clamp first; the sign of a -0.0 input, which the correction
-// steps lose, is put back from the input's sign bits.
+// half), divided by the block scale s (ns2 = {-s, -s}, r2 = {RN(1/s), RN(1/s)}).
+// |x / s| <= 448 (1 + eps) by construction of s, so the saturating conversion needs no clamp
+// first; the sign of a -0.0 input, which the correction steps lose, is put back from the
+// input's sign bits.
 __device__ __forceinline__ uint2 e4m3x8_div_bf16(const uint4& v, uint64_t ns2, uint64_t r2) {
   const uint32_t w[4] = {v.x, v.y, v.z, v.w};
   uint32_t c16[4];

@@ -103,3 +103,33 @@ def test_cpu_tensor_is_rejected():
     ops = _ops()
     with pytest.raises(RuntimeError):
         ops.quant_fp8_1x128(torch.zeros(4, 128, dtype=torch.bfloat16))
+
+
+def test_fp8_1x128_edge_values():
+    """Signed zeros, subnormals, the largest finite bf16, an all-zero block and exact e4m3
+    half-way quotients must come out bit-exact; in a block that holds an inf the finite elements
+    quantise to signed zeros and the scale is inf (x / inf)."""
+    from nanov41_b200 import ops
+    x = torch.zeros(4, 256, dtype=torch.float32)
+    x[0, :8] = torch.tensor([-0.0, 0.0, 1e-40, -1e-40, 3.3895e38, -3.3895e38, 1.0, -1.0])
+    x[0, 128:136] = torch.tensor([448.0, 416.0, 432.0, 0.5, 0.4375, 0.46875, -432.0, 13.0])  # ties
+    # row 1: all zeros (scale = 1e-4 / 448); row 2: small magnitudes below the 1e-4 floor
+    x[2, :128] = torch.linspace(-9e-5, 9e-5, 128)
+    x[2, 128:] = -0.0
+    x[3, :128] = torch.linspace(-3.0, 3.0, 128)
+    x = x.bfloat16()
+    codes, scales = ops.quant_fp8_1x128(x.cuda())
+    want_codes, want_scales = OQ.fp8_quant_1x128(x)
+    assert torch.equal(codes.cpu(), want_codes)
+    assert torch.equal(scales.cpu(), want_scales)
+    # a block with +inf: every finite element becomes +-0, scale inf
+    y = x.clone()
+    y[3, 5] = float("inf")
+    codes, scales = ops.quant_fp8_1x128(y.cuda())
+    c, s = codes.cpu(), scales.cpu()
+    assert torch.isinf(s[3, 0]) and torch.equal(s[:3], want_scales[:3]) and s[3, 1] == want_scales[3, 1]
+    finite = torch.ones(128, dtype=torch.bool)
+    finite[5] = False
+    neg = (y[3, :128].float() < 0) & finite
+    assert torch.all(c[3, :128][finite & ~neg] == 0x00) and torch.all(c[3, :128][neg] == 0x80)
+    assert torch.equal(c[:3], want_codes[:3]) and torch.equal(c[3, 128:], want_codes[3, 128:])
