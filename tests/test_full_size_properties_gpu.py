@@ -75,3 +75,28 @@ def test_forward_is_equivariant_under_token_permutation_at_config2(mode):
     ops.check_status()
     assert torch.isfinite(out.float()).all()
     assert torch.equal(out_p, out[perm])
+
+
+@pytest.mark.parametrize("fmt", [None, "ue8m0"])
+def test_backward_commutes_with_power_of_two_scaling_at_config2(fmt):
+    """Every step of the backward (1x128 quantisation of dOut, FP8 GEMMs with fp32 promotion,
+    SwiGLU backward, bf16 weight gradients) is exact under a power-of-two rescaling of dOut, so
+    all gradients for 4 dOut must be exactly 4 times those for dOut."""
+    from nanov41_b200 import autograd_moe, ops
+    c = make_case(**C2)
+    g = {n: t.cuda() for n, t in c.items()}
+    dout = torch.randn(C2["T"], C2["D"], generator=torch.Generator(device="cuda").manual_seed(9),
+                       device="cuda").bfloat16()
+
+    def grads(scale):
+        leaves = [g[n].clone().requires_grad_(True) for n in ("x", "weights", "w1", "w3", "w2")]
+        x, ws, w1, w3, w2 = leaves
+        out = autograd_moe.experts_forward(x, ws, g["indices"], w1, w3, w2, LIMIT, None, scale_fmt=fmt)
+        out.backward(dout * scale)
+        return [t.grad for t in leaves]
+
+    one, four = grads(1.0), grads(4.0)
+    ops.check_status()
+    for a, b, name in zip(one, four, ("dx", "dws", "dw1", "dw3", "dw2")):
+        assert torch.isfinite(a.float()).all(), name
+        assert torch.equal(a.float() * 4, b.float()), name
